@@ -1,0 +1,126 @@
+/*
+ * quarot_b200 -- C ABI of the B200 (sm_100a) quantized-linear kernels.
+ *
+ * Every entry point takes raw device pointers and sizes, enqueues work on the
+ * given CUDA stream of the CURRENT device, never allocates device memory,
+ * never synchronises the device and never throws.  Return value: 0 on success,
+ * a negative QR_E* code for an argument error, or a positive cudaError_t value
+ * if a CUDA call failed.  qr_last_error() returns a human-readable message for
+ * the most recent failure on the calling thread.
+ *
+ * Buffers are borrowed for the duration of the enqueued work; all matrices are
+ * row-major and densely packed unless a leading dimension is given.
+ * "int4 packed" means two signed 4-bit codes per byte, element 2j in the low
+ * nibble and element 2j+1 in the high nibble of byte j (the layout of
+ * pack_i4, quarot/functional/quantization.py:42-49, and of the upstream CUDA
+ * kernel, quarot/kernels/quant.cu:36-44 + quarot/kernels/include/int4.h:86-98).
+ *
+ * Each declaration cites the upstream interface it stands in for (paths are
+ * relative to the upstream QuaRot project).
+ */
+#ifndef QUAROT_B200_H
+#define QUAROT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define QR_VERSION 100
+
+enum {
+  QR_OK = 0,
+  QR_EINVAL = -1,      /* bad size / null pointer */
+  QR_EALIGN = -2,      /* pointer or leading dimension not aligned as documented */
+  QR_EUNSUPPORTED = -3,/* shape outside what the kernels implement */
+  QR_ENOTREADY = -4,   /* driver entry point missing (needs an sm_100 device + CUDA >= 12.8 driver) */
+  QR_EKERNEL = -5      /* a kernel reported a bounded-wait timeout (see qr_kernel_status) */
+};
+
+/* Library version (QR_VERSION) -- no upstream counterpart. */
+int qr_version(void);
+
+/* Message of the last failure on this thread ("" if none). Stands in for the
+ * C++ exceptions raised by TORCH_CHECK / ensure() upstream
+ * (quarot/kernels/bindings.cpp:11-16, quarot/kernels/include/common.h:16-23). */
+const char* qr_last_error(void);
+
+/* Reads (and clears) the device-side status word of the current device.
+ * Kernels with mbarrier waits give up after a bounded number of polls and set
+ * it instead of hanging; 0 means no kernel ever timed out.  Synchronises the
+ * device.  No upstream counterpart (upstream never checks launches). */
+int qr_kernel_status(int* status_out);
+
+/* Tuning knobs for experiments: key is e.g. "gemm_bn", "gemm_pst", "gemm_ist".
+ * Unknown keys return QR_EINVAL. No upstream counterpart. */
+int qr_set_tuning(const char* key, int value);
+
+/* ------------------------------------------------------------------ (a) ---
+ * Online Hadamard transform over the last axis, y = x (hadK (x) H_{n/K})^T/sqrt(n).
+ * Replaces fast_hadamard_transform.hadamard_transform + `hadK @` as called by
+ * matmul_hadU_cuda (quarot/functional/hadamard.py:92-101) and
+ * OnlineHadamard.forward (quarot/nn/hadamard.py:17-23).
+ *   x, y      : [rows, n] fp16 (f16 variant) or fp32 (f32 variant); y may alias x
+ *   had_k     : K x K row-major table of +-1 in fp16 on the device, or NULL when K == 1
+ *   K         : 1, or one of the table orders; n / K must be a power of two
+ * Internal arithmetic is fp32 in both variants; the result is rounded once. */
+int qr_hadamard_f16(const void* x, void* y, int64_t rows, int64_t n,
+                    const void* had_k, int K, void* stream);
+int qr_hadamard_f32(const float* x, float* y, int64_t rows, int64_t n,
+                    const void* had_k, int K, void* stream);
+
+/* Fused [online Hadamard ->] per-token absmax scale -> INT4 quantise -> pack.
+ * Replaces OnlineHadamard.forward + Quantizer.forward
+ * (quarot/nn/hadamard.py:17-23, quarot/nn/quantization.py:9-13) including the
+ * sym_quant kernel (quarot/kernels/quant.cu:11-61).
+ *   x        : [rows, n] fp16, row stride ldx elements (ldx % 8 == 0, 16-byte aligned)
+ *   K        : 0 = no Hadamard (quantiser only); 1 = Walsh; >1 = Kronecker with had_k
+ *   clip     : Quantizer.input_clip_ratio
+ *   q        : [rows, n/2] uint8 int4 packed          (n % 2 == 0)
+ *   scales   : [rows] fp16,  s = fp16(fp16(absmax/7) * clip)
+ *   y_out    : optional [rows, n] fp16 copy of the (rounded) Hadamard output that
+ *              was quantised, or NULL
+ * Codes are clamp(rint(fp16(y / s)), -8, 7) with the division in fp32, exactly
+ * the torch arithmetic of sym_quant (quarot/functional/quantization.py:29-32).
+ * A row whose absmax is 0 gets scale 0 and all-zero codes. */
+int qr_hadamard_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx,
+                         const void* had_k, int K, float clip,
+                         uint8_t* q, void* scales, void* y_out, void* stream);
+
+/* Standalone quantise-and-pack with caller-provided per-row scales.
+ * Replaces sym_quant_host (quarot/kernels/include/quant.h:6-13,
+ * quarot/kernels/quant.cu:48-61) behind quarot.sym_quant (quarot/__init__.py:43-46).
+ *   x [rows, cols] fp16, scale [rows] fp16, q [rows, ceil(cols/2)] uint8. */
+int qr_sym_quant_i4(const void* x, const void* scale, int64_t rows, int64_t cols,
+                    uint8_t* q, void* stream);
+
+/* ------------------------------------------------------------------ (b) ---
+ * C[M,N] int32 = unpack(A)[M,K] . unpack(B)[N,K]^T, exact.
+ * Replaces matmul_host (quarot/kernels/include/gemm.h:6-13,
+ * quarot/kernels/gemm.cu:7-46) behind quarot.matmul (quarot/__init__.py:37-41).
+ *   A [M, K/2], B [N, K/2] uint8 int4 packed, 16-byte aligned; K % 32 == 0. */
+int qr_matmul_i4_i32(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
+                     int32_t* C, void* stream);
+
+/* out[M,N] fp16 = s_row[m] * s_col[n] * half(q[m,n]), all products in fp16 in
+ * that order -- the arithmetic of sym_dequant_host
+ * (quarot/kernels/include/quant.h:15-23, quarot/kernels/quant.cu:64-97) behind
+ * quarot.sym_dequant (quarot/__init__.py:48-52). */
+int qr_sym_dequant_i32_f16(const int32_t* q, const void* scale_row, const void* scale_col,
+                           int64_t rows, int64_t cols, void* out, void* stream);
+
+/* Fused Linear4bit.forward (quarot/nn/linear.py:42-56): int4 GEMM with the
+ * dequantisation (and optional bias) applied in the epilogue, no int32 round
+ * trip through memory.
+ *   out[m,n] = fp16( float(acc[m,n]) * (float(sA[m]) * float(sB[n])) ) (+ bias[n] in fp16)
+ *   A [M,K/2], B [N,K/2] int4 packed; sA [M], sB [N], bias [N] or NULL: fp16;
+ *   out [M, N] fp16 with row stride ldo elements. */
+int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
+                     const void* bias, int64_t M, int64_t N, int64_t K,
+                     void* out, int64_t ldo, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QUAROT_B200_H */

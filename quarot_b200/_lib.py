@@ -1,0 +1,59 @@
+"""ctypes binding of libquarot_b200.so (the C-ABI declared in include/quarot_b200.h).
+
+The library is built in-tree by ``python -m quarot_b200.build``.  There is no
+fallback: if it is missing, importing this module raises.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libquarot_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        "quarot_b200: %s not found -- build it with `python -m quarot_b200.build` "
+        "(needs nvcc with sm_100a support); there is no non-CUDA fallback" % LIB_PATH)
+
+lib = ctypes.CDLL(LIB_PATH)
+
+_vp, _i64, _int, _f32 = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_float
+
+# name -> (restype, argtypes); must list every symbol of include/quarot_b200.h
+SIGNATURES = {
+    "qr_version": (_int, []),
+    "qr_last_error": (ctypes.c_char_p, []),
+    "qr_kernel_status": (_int, [ctypes.POINTER(_int)]),
+    "qr_set_tuning": (_int, [ctypes.c_char_p, _int]),
+    "qr_hadamard_f16": (_int, [_vp, _vp, _i64, _i64, _vp, _int, _vp]),
+    "qr_hadamard_f32": (_int, [_vp, _vp, _i64, _i64, _vp, _int, _vp]),
+    "qr_hadamard_quant_i4": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _f32, _vp, _vp, _vp, _vp]),
+    "qr_sym_quant_i4": (_int, [_vp, _vp, _i64, _i64, _vp, _vp]),
+    "qr_matmul_i4_i32": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
+    "qr_sym_dequant_i32_f16": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
+    "qr_linear_i4_f16": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+}
+
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error():
+    return lib.qr_last_error().decode("utf-8", "replace")
+
+
+def check(rc, what):
+    """Turn a non-zero status into the RuntimeError upstream raises from TORCH_CHECK."""
+    if rc != 0:
+        raise RuntimeError("%s failed (status %d): %s" % (what, rc, last_error()))
+
+
+def kernel_status():
+    out = _int(0)
+    check(lib.qr_kernel_status(ctypes.byref(out)), "qr_kernel_status")
+    return out.value
+
+
+def set_tuning(key, value):
+    check(lib.qr_set_tuning(key.encode(), int(value)), "qr_set_tuning")

@@ -1,0 +1,559 @@
+// Kernel family (b): INT4 x INT4 -> INT32 GEMM on the 5th-generation tensor cores
+// (tcgen05.mma kind::i8, accumulators in tensor memory), with the per-token x
+// per-channel dequantisation fused into the epilogue.
+//
+//   D[p, q] = sum_k  P[p, k] * Q[q, k]        P: [rowsP, K/2]  Q: [rowsQ, K/2]  int4 packed
+//
+// Both operands are K-major packed nibbles in global memory.  tcgen05 has no
+// 4-bit integer kind, so nibbles are widened to int8 in shared memory:
+//   * TMA (cp.async.bulk.tensor.2d) brings [rows x 64 B] packed tiles (128 K values
+//     per row) into a staging ring,
+//   * eight "widen" warps turn every 32-bit word w into  (w << 4) & 0xF0F0F0F0  (the
+//     four even elements) and  w & 0xF0F0F0F0  (the four odd elements): each nibble
+//     lands in the HIGH half of an int8, i.e. the value times 16 with the sign for
+//     free.  The accumulator is therefore exactly 256x the true dot product and the
+//     epilogue shifts it right by 8.  |acc| <= 64*K*256 < 2^31 for K <= 131071.
+//     Even/odd elements are written to separate 16-byte chunks: a fixed permutation of
+//     K applied to both operands alike, which leaves the dot product unchanged,
+//   * the int8 tiles use the canonical K-major 128-byte-swizzle layout (rows of 128 B,
+//     16-byte chunk index XOR (row & 7)), are published to the async proxy with
+//     fence.proxy.async and consumed by one thread issuing
+//     tcgen05.mma.cta_group::1.kind::i8 (M = 128, N = BN, K = 32 per instruction),
+//   * four epilogue warps read the accumulator with tcgen05.ld (32 lanes x 32 columns
+//     per warp), apply >> 8 and either store int32 or the fp16 dequantised value.
+// The kernel is persistent (static round-robin tile schedule) and, when ACC == 2,
+// double-buffers the accumulator so the epilogue of tile i overlaps the main loop
+// of tile i+1.
+//
+// SWAP = true serves decode-sized M: the weights become operand P (filling the 128
+// MMA rows) and the few token rows become operand Q (BN = 16..64); the epilogue then
+// writes the transposed tile.
+//
+// Every mbarrier wait is bounded: after kSpinLimit failed polls the waiting thread
+// raises a CTA-wide abort flag and the device status word, every role leaves its
+// loop, tensor memory is released and the kernel returns.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace qr {
+
+// ------------------------------------------------------------------ PTX
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+constexpr uint32_t kSpinLimit = 1u << 26;  // polls; several seconds at worst, never reached in a healthy run
+
+// Bounded wait.  Returns false if the CTA is aborting.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  atomicExch(status, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 B,
+// 8-row groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
+  d |= (uint64_t)0 << 16;                             // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024u >> 4) << 32;                  // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                             // version
+  d |= (uint64_t)2 << 61;                             // layout: SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor for kind::i8: signed 8-bit A and B, both K-major, int32 accumulate.
+__host__ __device__ constexpr uint32_t make_idesc_i8(int umma_m, int umma_n) {
+  return (2u << 4)                       // D format: S32
+         | (1u << 7)                     // A format: signed 8-bit
+         | (1u << 10)                    // B format: signed 8-bit
+         | (0u << 15) | (0u << 16)       // A, B K-major
+         | ((uint32_t)(umma_n >> 3) << 17)
+         | ((uint32_t)(umma_m >> 4) << 24);
+}
+
+// ------------------------------------------------------------------ kernel
+enum { MODE_I32 = 0, MODE_F16 = 1 };
+
+struct GemmParams {
+  int rowsP, rowsQ;      // valid rows of each operand
+  int K;                 // K elements (int4 values)
+  int tilesP, tilesQ;
+  void* out;             // int32 or fp16
+  int64_t ldo;           // elements
+  const __half* sP;      // per-row scale of operand P (fp16) or null (MODE_I32)
+  const __half* sQ;
+  const __half* bias;    // per output channel or null
+  int* status;
+};
+
+constexpr int kBM = 128;          // rows of operand P per tile = UMMA M
+constexpr int kBKBytes = 64;      // packed bytes per row per stage = 128 K values
+constexpr int kWidenWarps = 8;
+constexpr int kEpiWarps = 4;
+constexpr int kThreads = 32 * (2 + kEpiWarps + kWidenWarps);
+
+template <int BN, int PST, int IST>
+struct SmemLayout {
+  static constexpr int kI8Stage = (kBM + BN) * 128;
+  static constexpr int kPkStage = (kBM + BN) * kBKBytes;
+  static constexpr int kI8Off = 0;
+  static constexpr int kPkOff = IST * kI8Stage;
+  static constexpr int kBarOff = kPkOff + PST * kPkStage;
+  static constexpr int kNumBars = 2 * PST + 2 * IST + 4;
+  static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+  static constexpr int kAbortOff = kTmemSlotOff + 8;
+  static constexpr int kTotal = kAbortOff + 8;
+  static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
+};
+
+template <int BN, int PST, int IST, int ACC, bool SWAP, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
+  using L = SmemLayout<BN, PST, IST>;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const uint32_t bar_base = smem_base + L::kBarOff;
+  auto full_p = [&](int s) { return bar_base + 8u * s; };
+  auto empty_p = [&](int s) { return bar_base + 8u * (PST + s); };
+  auto full_i = [&](int s) { return bar_base + 8u * (2 * PST + s); };
+  auto empty_i = [&](int s) { return bar_base + 8u * (2 * PST + IST + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
+
+  constexpr uint32_t kTmemCols = (ACC * BN) < 32 ? 32 : (ACC * BN);
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps); }
+    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), kWidenWarps); mbar_init(empty_i(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), kEpiWarps); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_base + L::kTmemSlotOff, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tilesP * p.tilesQ;
+  const int num_kb = (p.K + 127) >> 7;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int tp = tile % p.tilesP, tq = tile / p.tilesP;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % PST;
+          const uint32_t ph = (it / PST) & 1;
+          if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          mbar_expect_tx(full_p(s), L::kPkStage);
+          const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
+          tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * kBM);
+          tma_load_2d(dst + kBM * kBKBytes, &tmQ, full_p(s), kb * kBKBytes, tq * BN);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(kBM, BN);
+      uint32_t it = 0, tl = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
+        const int a = tl % ACC;
+        const uint32_t pha = (tl / ACC) & 1;
+        if (!mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % IST;
+          const uint32_t ph = (it / IST) & 1;
+          if (!mbar_wait(full_i(s), ph, abort_flag, p.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + L::kI8Off + s * L::kI8Stage;
+          const uint64_t da = make_kmajor_sw128_desc(a_addr);
+          const uint64_t db = make_kmajor_sw128_desc(a_addr + kBM * 128);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
+            umma_i8(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_i(s));
+        }
+        if (ok) umma_commit(acc_full(a));
+      }
+    }
+  } else if (warp < 2 + kEpiWarps) {
+    // ------------------------------------------------------------ epilogue
+    const int q4 = warp & 3;                 // TMEM lane quarter this warp may access
+    const int prow_in_tile = q4 * 32 + lane; // accumulator row owned by this thread
+    uint32_t tl = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
+      const int tp = tile % p.tilesP, tq = tile / p.tilesP;
+      const int a = tl % ACC;
+      const uint32_t pha = (tl / ACC) & 1;
+      if (!mbar_wait(acc_full(a), pha, abort_flag, p.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      const int prow = tp * kBM + prow_in_tile;
+      const bool prow_ok = prow < p.rowsP;
+      float sp = 0.0f;
+      if (MODE == MODE_F16 && prow_ok) sp = __half2float(p.sP[prow]);
+      constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += CH) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * BN + c0);
+        if (CH == 32) tmem_ld32(taddr, r); else tmem_ld16(taddr, r);
+        tmem_ld_wait();
+        if (c0 + CH >= BN) {
+          // accumulator fully read: hand the TMEM buffer back to the MMA warp
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty(a));
+        }
+        const int qcol0 = tq * BN + c0;
+        if (!SWAP) {
+          // thread owns output row `prow` (a token), columns qcol0.. (output channels)
+          if (prow_ok) {
+            if (MODE == MODE_I32) {
+              int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
+              if (qcol0 + CH <= p.rowsQ && (p.ldo & 3) == 0) {
+#pragma unroll
+                for (int j = 0; j < CH; j += 4)
+                  *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
+                                                              (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CH; ++j)
+                  if (qcol0 + j < p.rowsQ) o[j] = (int32_t)r[j] >> 8;
+              }
+            } else {
+              __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
+              const bool full = (qcol0 + CH <= p.rowsQ) && ((p.ldo & 7) == 0);
+              if (full) {
+#pragma unroll
+                for (int j = 0; j < CH; j += 8) {
+                  uint4 pk;
+                  __half2* h = reinterpret_cast<__half2*>(&pk);
+                  const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + j));
+                  const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 sc = __half22float2(sqh[e]);
+                    const float v0 = (float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x);
+                    const float v1 = (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y);
+                    h[e] = __floats2half2_rn(v0, v1);
+                  }
+                  if (p.bias) {
+                    const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + j));
+                    const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
+                  }
+                  *reinterpret_cast<uint4*>(o + j) = pk;
+                }
+              } else {
+#pragma unroll
+                for (int j = 0; j < CH; ++j) {
+                  if (qcol0 + j < p.rowsQ) {
+                    const float sc = __half2float(p.sQ[qcol0 + j]);
+                    __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sp * sc));
+                    if (p.bias) v = __hadd(v, p.bias[qcol0 + j]);
+                    o[j] = v;
+                  }
+                }
+              }
+            }
+          }
+        } else {
+          // SWAP: thread owns output channel `prow`; columns are token rows qcol0..
+          if (prow_ok) {
+#pragma unroll
+            for (int j = 0; j < CH; ++j) {
+              const int tok = qcol0 + j;
+              if (tok < p.rowsQ) {
+                if (MODE == MODE_I32) {
+                  reinterpret_cast<int32_t*>(p.out)[(int64_t)tok * p.ldo + prow] = (int32_t)r[j] >> 8;
+                } else {
+                  const float sc = __half2float(__ldg(p.sQ + tok));
+                  __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sc * sp));
+                  if (p.bias) v = __hadd(v, p.bias[prow]);
+                  reinterpret_cast<__half*>(p.out)[(int64_t)tok * p.ldo + prow] = v;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ widen int4 -> int8
+    const int wt = threadIdx.x - 32 * (2 + kEpiWarps);  // 0 .. 255
+    constexpr int kChunks = (kBM + BN) * 4;             // 16-byte packed chunks per stage
+    constexpr int kWThreads = 32 * kWidenWarps;
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int sp_ = it % PST, si = it % IST;
+        const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
+        if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 5)) { ok = false; break; }
+        if (!mbar_wait(empty_i(si), phi ^ 1, abort_flag, p.status, 6)) { ok = false; break; }
+        tc_fence_after();
+        const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
+        unsigned char* i8 = smem_gen + L::kI8Off + si * L::kI8Stage;
+#pragma unroll
+        for (int c = wt; c < kChunks; c += kWThreads) {
+          const int row = c >> 2, cc = c & 3;
+          const uint4 w = *reinterpret_cast<const uint4*>(pk + c * 16);
+          uint4 lo, hi;
+          lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;
+          lo.y = (w.y << 4) & 0xF0F0F0F0u; hi.y = w.y & 0xF0F0F0F0u;
+          lo.z = (w.z << 4) & 0xF0F0F0F0u; hi.z = w.z & 0xF0F0F0F0u;
+          lo.w = (w.w << 4) & 0xF0F0F0F0u; hi.w = w.w & 0xF0F0F0F0u;
+          unsigned char* drow = i8 + row * 128;
+          const int sw = row & 7;
+          *reinterpret_cast<uint4*>(drow + (((2 * cc) ^ sw) << 4)) = lo;
+          *reinterpret_cast<uint4*>(drow + (((2 * cc + 1) ^ sw) << 4)) = hi;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(full_i(si));
+          mbar_arrive(empty_p(sp_));
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Tensor map over a packed int4 matrix [rows, kbytes] (uint8), box = [64 bytes, box_rows], no swizzle.
+static int make_packed_map(CUtensorMap* map, const void* base, int64_t rows, int64_t kbytes, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(QR_ENOTREADY, "cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)kbytes};
+  cuuint32_t box[2] = {(cuuint32_t)kBKBytes, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(QR_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return QR_OK;
+}
+
+template <int BN, int PST, int IST, int ACC, bool SWAP, int MODE>
+static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
+  using L = SmemLayout<BN, PST, IST>;
+  static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
+  auto kern = gemm_i4_kernel<BN, PST, IST, ACC, SWAP, MODE>;
+  static thread_local bool configured[64] = {false};
+  int dev = 0;
+  QR_CUDA(cudaGetDevice(&dev));
+  if (dev >= 64 || !configured[dev]) {
+    QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
+    if (dev < 64) configured[dev] = true;
+  }
+  int grid = p.tilesP * p.tilesQ;
+  int cap = grid_cap > 0 ? grid_cap : num_sms();
+  if (grid > cap) grid = cap;
+  kern<<<grid, kThreads, L::kDynamic, st>>>(tmP, tmQ, p);
+  QR_LAUNCH_CHECK("gemm_i4_kernel");
+  return QR_OK;
+}
+
+template <int MODE>
+static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
+                    void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st) {
+  if (M < 0 || N < 0 || K < 0) return fail(QR_EINVAL, "%s: negative size", who);
+  if (M == 0 || N == 0) return QR_OK;
+  if (!A || !B || !out) return fail(QR_EINVAL, "%s: null pointer", who);
+  if (MODE == MODE_F16 && (!sA || !sB)) return fail(QR_EINVAL, "%s: null scale pointer", who);
+  if (K == 0 || (K % 32) != 0) return fail(QR_EINVAL, "%s: K = %lld must be a positive multiple of 32", who, (long long)K);
+  if (K > 131071) return fail(QR_EUNSUPPORTED, "%s: K = %lld exceeds the int32 headroom of the x256 accumulator", who, (long long)K);
+  if (M > (1 << 30) || N > (1 << 30)) return fail(QR_EUNSUPPORTED, "%s: dimension too large", who);
+  if (!aligned16(A) || !aligned16(B)) return fail(QR_EALIGN, "%s: operands must be 16-byte aligned", who);
+  if (ldo < N) return fail(QR_EINVAL, "%s: ldo < N", who);
+  int* status = kernel_status_ptr();
+  if (!status) return fail(QR_ENOTREADY, "%s: no CUDA device", who);
+
+  const int swap_max_m = tuning("gemm_swap_max_m", 64);
+  const bool swap = M <= swap_max_m;
+  GemmParams p;
+  p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
+  p.bias = reinterpret_cast<const __half*>(bias);
+  CUtensorMap tmP, tmQ;
+  int rc;
+  const int grid_cap = tuning("gemm_grid", 0);
+  if (!swap) {
+    int bn = tuning("gemm_bn", 256);
+    if (bn != 256 && bn != 128 && bn != 64) bn = 256;
+    p.rowsP = (int)M; p.rowsQ = (int)N;
+    p.tilesP = (int)((M + kBM - 1) / kBM); p.tilesQ = (int)((N + bn - 1) / bn);
+    p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
+    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
+    if ((rc = make_packed_map(&tmQ, B, N, K / 2, bn))) return rc;
+    const int pst = tuning("gemm_pst", 4);
+    if (bn == 256) {
+      if (pst == 3) return launch_gemm<256, 3, 3, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
+      return launch_gemm<256, 4, 2, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
+    }
+    if (bn == 128) return launch_gemm<128, 4, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
+    return launch_gemm<64, 6, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
+  }
+  // decode-sized M: weights fill the MMA rows, tokens are the MMA columns
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  p.rowsP = (int)N; p.rowsQ = (int)M;
+  p.tilesP = (int)((N + kBM - 1) / kBM); p.tilesQ = (int)((M + bn - 1) / bn);
+  p.sP = reinterpret_cast<const __half*>(sB); p.sQ = reinterpret_cast<const __half*>(sA);
+  if ((rc = make_packed_map(&tmP, B, N, K / 2, kBM))) return rc;
+  if ((rc = make_packed_map(&tmQ, A, M, K / 2, bn))) return rc;
+  if (bn == 16) return launch_gemm<16, 8, 4, 2, true, MODE>(tmP, tmQ, p, grid_cap, st);
+  if (bn == 32) return launch_gemm<32, 8, 4, 2, true, MODE>(tmP, tmQ, p, grid_cap, st);
+  return launch_gemm<64, 6, 4, 2, true, MODE>(tmP, tmQ, p, grid_cap, st);
+}
+
+}  // namespace qr
+
+extern "C" {
+
+int qr_matmul_i4_i32(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, int32_t* C, void* stream) {
+  return qr::run_gemm<qr::MODE_I32>("qr_matmul_i4_i32", A, B, M, N, K, C, N, nullptr, nullptr, nullptr,
+                                    (cudaStream_t)stream);
+}
+
+int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
+                     int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
+  return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16", A, B, M, N, K, out, ldo, sA, sB, bias,
+                                    (cudaStream_t)stream);
+}
+
+}  // extern "C"

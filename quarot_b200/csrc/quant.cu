@@ -1,0 +1,147 @@
+// Standalone quantise-and-pack (caller-provided scales) and int32 -> fp16 dequantise.
+// Both are pure streaming kernels: one 16-byte load -> one 4-byte store (quant),
+// one 16-byte load -> one 8-byte store (dequant).
+#include "common.cuh"
+
+namespace qr {
+
+// Eight fp16 values (one uint4) -> four packed bytes.
+__device__ __forceinline__ uint32_t quant8(const uint4& v, float s, float rcp) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __half22float2(h[i]);
+    uint32_t c = quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp));
+    // c: code(2i) in bits 3:0, code(2i+1) in bits 19:16  ->  byte i = lo | hi << 4
+    out |= ((c & 0xF) | ((c >> 12) & 0xF0)) << (8 * i);
+  }
+  return out;
+}
+
+__global__ void __launch_bounds__(256)
+sym_quant_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ scale,
+                     int64_t rows, int64_t cols, uint8_t* __restrict__ q) {
+  // cols % 8 == 0: every thread owns 8 consecutive elements of one row
+  const int64_t vec_per_row = cols >> 3;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / vec_per_row;
+    const float s = __half2float(scale[row]);
+    uint4 v = *reinterpret_cast<const uint4*>(x + i * 8);
+    uint32_t packed = 0;
+    if (s != 0.0f) packed = quant8(v, s, __frcp_rn(s));
+    *reinterpret_cast<uint32_t*>(q + i * 4) = packed;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+sym_quant_scalar_kernel(const __half* __restrict__ x, const __half* __restrict__ scale,
+                        int64_t rows, int64_t cols, int64_t cols_dst, uint8_t* __restrict__ q) {
+  // any cols (also odd): one thread per output byte
+  const int64_t total = rows * cols_dst;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / cols_dst;
+    const int64_t c = (i - row * cols_dst) * 2;
+    const float s = __half2float(scale[row]);
+    uint32_t byte = 0;
+    if (s != 0.0f) {
+      const float rcp = __frcp_rn(s);
+      float a = __half2float(x[row * cols + c]);
+      float b = (c + 1 < cols) ? __half2float(x[row * cols + c + 1]) : 0.0f;
+      uint32_t code = quant_pair(div_by_scale(a, s, rcp), div_by_scale(b, s, rcp));
+      byte = (code & 0xF) | ((code >> 12) & 0xF0);
+    }
+    q[i] = (uint8_t)byte;
+  }
+}
+
+// out = (s_row * s_col) * half(q), every product rounded to fp16, in that order.
+__global__ void __launch_bounds__(256)
+sym_dequant_vec_kernel(const int32_t* __restrict__ q, const __half* __restrict__ srow,
+                       const __half* __restrict__ scol, int64_t rows, int64_t cols,
+                       __half* __restrict__ out) {
+  const int64_t vec_per_row = cols >> 2;
+  const int64_t total = rows * vec_per_row;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / vec_per_row;
+    const int64_t c = (i - row * vec_per_row) * 4;
+    const int4 v = *reinterpret_cast<const int4*>(q + row * cols + c);
+    const __half sr = srow[row];
+    const __half2 sc01 = *reinterpret_cast<const __half2*>(scol + c);
+    const __half2 sc23 = *reinterpret_cast<const __half2*>(scol + c + 2);
+    __half2 r01 = __hmul2(__hmul2(__half2half2(sr), sc01),
+                          __halves2half2(__int2half_rn(v.x), __int2half_rn(v.y)));
+    __half2 r23 = __hmul2(__hmul2(__half2half2(sr), sc23),
+                          __halves2half2(__int2half_rn(v.z), __int2half_rn(v.w)));
+    uint2 o;
+    o.x = *reinterpret_cast<uint32_t*>(&r01);
+    o.y = *reinterpret_cast<uint32_t*>(&r23);
+    *reinterpret_cast<uint2*>(out + row * cols + c) = o;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+sym_dequant_scalar_kernel(const int32_t* __restrict__ q, const __half* __restrict__ srow,
+                          const __half* __restrict__ scol, int64_t rows, int64_t cols,
+                          __half* __restrict__ out) {
+  const int64_t total = rows * cols;
+  for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / cols;
+    const int64_t c = i - row * cols;
+    out[i] = __hmul(__hmul(srow[row], scol[c]), __int2half_rn(q[i]));
+  }
+}
+
+static int grid_for(int64_t total_threads) {
+  int64_t blocks = (total_threads + 255) / 256;
+  int64_t cap = (int64_t)num_sms() * 16;
+  if (blocks < 1) blocks = 1;
+  return (int)(blocks < cap ? blocks : cap);
+}
+
+}  // namespace qr
+
+extern "C" {
+
+int qr_sym_quant_i4(const void* x, const void* scale, int64_t rows, int64_t cols,
+                    uint8_t* q, void* stream) {
+  if (rows < 0 || cols < 0) return qr::fail(QR_EINVAL, "qr_sym_quant_i4: negative size");
+  if (rows == 0 || cols == 0) return QR_OK;
+  if (!x || !scale || !q) return qr::fail(QR_EINVAL, "qr_sym_quant_i4: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((cols & 7) == 0 && qr::aligned16(x) && ((uintptr_t)q & 3) == 0) {
+    qr::sym_quant_vec_kernel<<<qr::grid_for(rows * (cols >> 3)), 256, 0, st>>>(
+        (const __half*)x, (const __half*)scale, rows, cols, q);
+  } else {
+    const int64_t cd = (cols + 1) / 2;
+    qr::sym_quant_scalar_kernel<<<qr::grid_for(rows * cd), 256, 0, st>>>(
+        (const __half*)x, (const __half*)scale, rows, cols, cd, q);
+  }
+  QR_LAUNCH_CHECK("qr_sym_quant_i4");
+  return QR_OK;
+}
+
+int qr_sym_dequant_i32_f16(const int32_t* q, const void* scale_row, const void* scale_col,
+                           int64_t rows, int64_t cols, void* out, void* stream) {
+  if (rows < 0 || cols < 0) return qr::fail(QR_EINVAL, "qr_sym_dequant_i32_f16: negative size");
+  if (rows == 0 || cols == 0) return QR_OK;
+  if (!q || !scale_row || !scale_col || !out)
+    return qr::fail(QR_EINVAL, "qr_sym_dequant_i32_f16: null pointer");
+  cudaStream_t st = (cudaStream_t)stream;
+  if ((cols & 3) == 0 && qr::aligned16(q) && ((uintptr_t)out & 7) == 0 && ((uintptr_t)scale_col & 3) == 0) {
+    qr::sym_dequant_vec_kernel<<<qr::grid_for(rows * (cols >> 2)), 256, 0, st>>>(
+        q, (const __half*)scale_row, (const __half*)scale_col, rows, cols, (__half*)out);
+  } else {
+    qr::sym_dequant_scalar_kernel<<<qr::grid_for(rows * cols), 256, 0, st>>>(
+        q, (const __half*)scale_row, (const __half*)scale_col, rows, cols, (__half*)out);
+  }
+  QR_LAUNCH_CHECK("qr_sym_dequant_i32_f16");
+  return QR_OK;
+}
+
+}  // extern "C"

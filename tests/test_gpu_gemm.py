@@ -1,0 +1,175 @@
+"""CUDA kernels of family (b) -- int4 GEMM (tcgen05) and the fused dequant epilogue --
+against the CPU oracle and the upstream-generated fixtures, through the C-ABI."""
+import numpy as np
+import pytest
+import torch
+
+import quarot_b200 as qb
+from quarot_b200 import _lib, synth
+from quarot_b200.functional.quantization import pack_i4
+from oracle import quarot_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _rand_packed(rows, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    return pack_i4(torch.randint(-8, 8, (rows, k), generator=g, dtype=torch.int8))
+
+
+def test_matmul_matches_upstream_fixtures(golden):
+    g = golden["matmul"]
+    for t in ("s", "m", "l"):
+        a, b = torch.from_numpy(g[t + "_a"]).to(DEV), torch.from_numpy(g[t + "_b"]).to(DEV)
+        c = qb.matmul(a, b).cpu()
+        assert c.dtype == torch.int32 and np.array_equal(c.numpy(), g[t + "_c"]), t
+    assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (3, 7, 32), (8, 4096, 4096), (16, 128, 96), (17, 130, 256),
+                                   (32, 272, 1024), (33, 48, 160), (64, 256, 4096), (65, 256, 128),
+                                   (128, 256, 128), (129, 257, 224), (130, 272, 1024), (256, 512, 11008),
+                                   (300, 1000, 2048), (512, 384, 28672)])
+def test_matmul_bit_exact_random_shapes(M, N, K):
+    a, b = _rand_packed(M, K, M * 3 + K), _rand_packed(N, K, N * 5 + K)
+    c = qb.matmul(a.to(DEV), b.to(DEV)).cpu()
+    assert torch.equal(c, O.matmul_i4(a, b))
+    assert _lib.kernel_status() == 0
+
+
+def test_matmul_extreme_codes_no_overflow():
+    # all -8 x all -8 is the largest accumulator: 64 K (x256 inside the kernel)
+    K = 28672
+    a = torch.full((130, K // 2), 0x88, dtype=torch.uint8)
+    b = torch.full((40, K // 2), 0x88, dtype=torch.uint8)
+    c = qb.matmul(a.to(DEV), b.to(DEV)).cpu()
+    assert int(c.min()) == int(c.max()) == 64 * K
+    b7 = torch.full((40, K // 2), 0x77, dtype=torch.uint8)
+    c = qb.matmul(a.to(DEV), b7.to(DEV)).cpu()
+    assert int(c.min()) == int(c.max()) == -56 * K
+
+
+def test_matmul_leading_dims_and_errors():
+    a, b = _rand_packed(2 * 3, 128, 1).view(2, 3, 64), _rand_packed(5, 128, 2)
+    c = qb.matmul(a.to(DEV), b.to(DEV))
+    assert c.shape == (2, 3, 5)
+    assert torch.equal(c.cpu().view(6, 5), O.matmul_i4(a.view(6, 64), b))
+    with pytest.raises(AssertionError):
+        qb.matmul(torch.zeros(2, 24, dtype=torch.uint8, device=DEV), b.to(DEV))
+    with pytest.raises(RuntimeError):
+        qb.matmul(a.to(DEV), torch.zeros(5, 32, dtype=torch.uint8, device=DEV))
+    with pytest.raises(RuntimeError):
+        qb.matmul(a.to(DEV).transpose(0, 1), b.to(DEV))
+
+
+@pytest.mark.parametrize("tiles", ["bn128", "bn64", "pst3", "grid3"])
+def test_matmul_other_tile_configs_agree(tiles):
+    key, val = {"bn128": ("gemm_bn", 128), "bn64": ("gemm_bn", 64), "pst3": ("gemm_pst", 3), "grid3": ("gemm_grid", 3)}[tiles]
+    a, b = _rand_packed(300, 2048, 1), _rand_packed(1000, 2048, 2)
+    want = O.matmul_i4(a, b)
+    _lib.set_tuning(key, val)
+    try:
+        c = qb.matmul(a.to(DEV), b.to(DEV)).cpu()
+    finally:
+        _lib.set_tuning(key, 256 if key == "gemm_bn" else (4 if key == "gemm_pst" else 0))
+    assert torch.equal(c, want)
+    assert _lib.kernel_status() == 0
+
+
+def _linear_close(out, ref):
+    err = (out.double() - ref.double()).abs()
+    tol = 1e-2 * ref.double().abs() + 1e-2 * float(ref.abs().max()) * 2.0 ** -10
+    return bool((err <= tol).all()), float((err / (ref.double().abs() + 1e-6)).max())
+
+
+@pytest.mark.parametrize("M,N,K,bias", [(1, 4096, 4096, False), (8, 256, 4096, True), (32, 272, 1024, False),
+                                        (64, 512, 11008, True), (129, 257, 224, True), (256, 4096, 4096, False),
+                                        (300, 1000, 2048, True)])
+def test_linear_fused_dequant_vs_fp32_oracle(M, N, K, bias):
+    g = torch.Generator().manual_seed(M + N)
+    a, w = _rand_packed(M, K, 3), _rand_packed(N, K, 4)
+    sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand(N, 1, generator=g) * 0.015 + 0.005).half()
+    bvec = (torch.randn(N, generator=g) * 0.5).half() if bias else None
+    out = qb.linear_i4(a.to(DEV), sx.to(DEV), w.to(DEV), sw.to(DEV), bvec.to(DEV) if bias else None).cpu()
+    ref = O.sym_dequant_fp32(O.matmul_i4(a, w), sx, sw)
+    if bias:
+        # upstream adds the bias in fp16 after rounding the product
+        assert torch.equal(out, ref.half() + bvec)
+    else:
+        ok, worst = _linear_close(out, ref)
+        assert ok, worst
+        # one fp32 product rounded once: identical to the fp32 oracle rounded to fp16
+        assert torch.equal(out, ref.half())
+    assert _lib.kernel_status() == 0
+
+
+def test_module_graph_config0_slice():
+    """Sequential(OnlineHadamard, Quantizer, Linear4bit) as the callers build it, 256 token rows of config 0."""
+    M, K, N = 256, 4096, 4096
+    x = synth.activations(M, K, seed=1234)
+    w, sw = synth.weights(N, K, seed=4321)
+    lin = qb.nn.Linear4bit(K, N).to(DEV)
+    lin.weight.copy_(w)
+    lin.weight_scales = sw.to(DEV)
+    seq = torch.nn.Sequential(qb.nn.OnlineHadamard(K), qb.nn.Quantizer(), lin).to(DEV)
+    out = seq(x.to(DEV).view(2, 128, K))
+    assert out.shape == (2, 128, N) and out.dtype == torch.float16
+    # oracle fed with the kernel's own Hadamard output
+    y = seq[0](x.to(DEV)).cpu()
+    s = O.quantizer_scales(y)
+    acc = O.matmul_i4(O.pack_i4(O.sym_quant_codes(y, s)), w)
+    ref = O.sym_dequant_fp32(acc, s, sw)
+    assert torch.equal(out.cpu().view(M, N), ref.half())
+    # int32 path of the unfused operators agrees bit for bit
+    p = seq[1](seq[0](x.to(DEV)))
+    assert torch.equal(qb.matmul(p.quantized_x, lin.weight).cpu(), acc)
+    # and the whole thing is within 1e-2 of the fp32 reference built from the fp32 Hadamard
+    full = O.linear4bit_forward(x, w, sw, hadamard_dim=K)
+    rel = (out.cpu().view(M, N).float() - full["out"]).norm() / full["out"].norm()
+    assert float(rel) < 1e-2
+    # fused module rewrite gives the same output
+    assert qb.nn.fuse_modules(seq) == 1
+    assert torch.equal(seq(x.to(DEV).view(2, 128, K)), out)
+    assert _lib.kernel_status() == 0
+
+
+def test_from_float_roundtrip():
+    g = torch.Generator().manual_seed(2)
+    lin = torch.nn.Linear(256, 64, bias=True).half()
+    codes = torch.randint(-8, 8, (64, 256), generator=g).half()
+    s_w = (torch.rand(64, 1, generator=g) * 0.01 + 0.005).half()
+    lin.weight.data = codes * s_w
+    q = qb.nn.Linear4bit.from_float(lin, weight_scales=s_w).to(DEV)
+    assert torch.equal(O.unpack_i4(q.weight.cpu()).half(), codes)
+    x = synth.activations(9, 256, seed=1).to(DEV)
+    out = torch.nn.Sequential(qb.nn.Quantizer(), q)(x)
+    ref = O.linear4bit_forward(x.cpu(), q.weight.cpu(), s_w, bias=lin.bias.data)
+    assert torch.allclose(out.cpu().float(), ref["out"], rtol=4e-3, atol=4e-3)
+    rnd = qb.nn.Linear4bit.from_float(torch.nn.Linear(64, 8, bias=False).half())
+    assert float(rnd.weight_scales.abs().max()) == 0.0
+
+
+def test_full_size_config0_properties():
+    """BASELINE config 0 at full size: checksum identity over all 8.4 M accumulators plus sampled rows."""
+    M, K, N = 2048, 4096, 4096
+    x = synth.activations(M, K, seed=1234).to(DEV)
+    w, sw = synth.weights(N, K, seed=4321)
+    q, s, y = qb.hadamard_quant(x, None, 1, 1.0, return_y=True)
+    acc = qb.matmul(q, w.to(DEV))
+    # sum_mn C[m,n] == sum_k (sum_m A[m,k]) (sum_n B[n,k])
+    ua, ub = O.unpack_i4(q.cpu()).long(), O.unpack_i4(w).long()
+    assert int(acc.long().sum()) == int((ua.sum(0) * ub.sum(0)).sum())
+    rows = torch.arange(0, M, 37)
+    assert torch.equal(acc.cpu()[rows], O.matmul_i4(q.cpu()[rows], w))
+    # codes bit-exact for the sampled rows given the kernel's Hadamard output
+    s_ref = O.quantizer_scales(y.cpu()[rows])
+    assert torch.equal(s.cpu()[rows], s_ref)
+    assert torch.equal(q.cpu()[rows], O.pack_i4(O.sym_quant_codes(y.cpu()[rows], s_ref)))
+    out = qb.linear_i4(q, s, w.to(DEV), sw.to(DEV))
+    ref = O.sym_dequant_fp32(acc.cpu()[rows], s_ref, sw)
+    assert torch.equal(out.cpu()[rows], ref.half())
+    # determinism: a second run is bitwise identical
+    assert torch.equal(qb.linear_i4(q, s, w.to(DEV), sw.to(DEV)), out)
+    assert _lib.kernel_status() == 0
