@@ -1,0 +1,411 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path (Hadamard + int4 quantise + int4 GEMM + dequant).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A "step" is one pass over the linears of one decoder layer for one batch of
+token rows: per linear, kernel (a) (fused [Hadamard ->] absmax -> int4 pack) and
+kernel (b) (tcgen05 int4 GEMM with the dequant epilogue).  The default workload is
+the LLaMA-2-7B layer at prefill size (M = 2048 tokens): QKV 4096->12288, o_proj
+4096->4096, gate/up 4096->22016 (quantiser only) and down_proj 11008->4096 with
+the online Hadamard had_172 (x) Walsh_64.  Activations and weights are seeded
+synthetic tensors with the benchmark's value distributions (quarot_b200/synth.py).
+
+N > 1 (launched with torch.distributed.run, one rank per GPU): token rows are
+sharded, weights replicated, no collective on the data path; every rank processes
+M rows per step (weak scaling) and the reported value is the whole-job aggregate.
+
+One JSON line is printed by rank 0.  --impl reference times the CPU restatement of
+the upstream torch path (oracle/) on the host cores for the same metric and config.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (layer table name, default tokens per GPU)
+    "llama2_7b_prefill": ("LLAMA2_7B", 2048),
+    "config0": ("CONFIG0", 2048),
+    "llama2_7b_decode": ("LLAMA2_7B", 32),
+    "llama2_70b_prefill": ("LLAMA2_70B", 4096),
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+def layer_ops(layers, M):
+    return sum(2.0 * M * N * K for (_, K, N, _) in layers)
+
+
+def bytes_quant(M, K):
+    return 2.0 * M * K + M * K / 2.0 + 2.0 * M
+
+
+def bytes_gemm(M, K, N):
+    return M * K / 2.0 + N * K / 2.0 + 2.0 * M + 2.0 * N + 2.0 * M * N
+
+
+# ------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------ reference (CPU) arm
+def cpu_reference_run(layers, M_full, steps, warmup, budget_s=20.0):
+    """Times the CPU restatement of the upstream torch path on a bounded sample of token rows.
+
+    Weights are unpacked to int32 once, outside the timed region (as the fake-quant
+    reference keeps them); per step and per linear: Hadamard (fp32 butterflies, cast
+    to fp16), per-token scale, quantise, pack, unpack, int32 matmul, fp32 dequant.
+    """
+    from oracle import quarot_oracle as O
+    from quarot_b200 import synth
+    cores = torch.get_num_threads()
+    # pick the sample so that one step costs about budget_s / (steps + warmup)
+    a = torch.randint(-8, 8, (16, 4096), dtype=torch.int32)
+    b = torch.randint(-8, 8, (1024, 4096), dtype=torch.int32)
+    t0 = time.perf_counter()
+    _ = a @ b.T
+    rate = 2.0 * 16 * 1024 * 4096 / max(time.perf_counter() - t0, 1e-6)   # int ops / s
+    per_token_ops = layer_ops(layers, 1)
+    target = budget_s / max(steps + warmup, 1)
+    ms = int(max(1, min(64, M_full, rate * target / per_token_ops)))
+    data = []
+    for (name, K, N, had) in layers:
+        x = synth.activations(ms, K, seed=1234)
+        w, sw = synth.weights(N, K, seed=4321)
+        data.append((x, O.unpack_i4(w), sw, had))
+
+    def step():
+        outs = []
+        for (x, wu, sw, had) in data:
+            y = O.hadamard(x.float()).to(torch.float16) if had else x
+            s = O.quantizer_scales(y)
+            p = O.pack_i4(O.sym_quant_codes(y, s))
+            acc = O.unpack_i4(p) @ wu.T
+            outs.append(O.sym_dequant_fp32(acc, s, sw).to(torch.float16))
+        return outs
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / max(steps, 1)
+    tops = layer_ops(layers, ms) / dt / 1e12
+    return {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
+            "sample": "%d of %d token rows per step, %d steps; weights pre-unpacked to int32 outside the "
+                      "timed region; ms_per_step is scaled linearly to %d rows" % (ms, M_full, steps, M_full),
+            "ms_per_step_full": dt * 1e3 * (M_full / ms), "tokens_per_s": ms / dt}
+
+
+# ------------------------------------------------------------------ device arm
+def build_device_workload(layers, M, dev, nsets):
+    import quarot_b200 as qb
+    from quarot_b200 import synth
+    from quarot_b200.functional import hadamard as FH
+    work = []
+    for li, (name, K, N, had) in enumerate(layers):
+        khad = FH.get_hadK(K)[1] if had else 0
+        table = FH.device_table(khad, dev) if khad > 1 else None
+        xs = [synth.activations_device(M, K, seed=1234 + 17 * s + li, device=dev) for s in range(nsets)]
+        ws = [synth.weights_device(N, K, seed=4321 + 13 * s + li, device=dev) for s in range(nsets)]
+        work.append({
+            "name": name, "K": K, "N": N, "khad": khad, "table": table, "x": xs,
+            "w": [w for (w, _) in ws], "sw": [s.view(-1).contiguous() for (_, s) in ws],
+            "q": torch.empty((M, K // 2), dtype=torch.uint8, device=dev),
+            "s": torch.empty((M,), dtype=torch.float16, device=dev),
+            "out": torch.empty((M, N), dtype=torch.float16, device=dev),
+        })
+    return work
+
+
+def device_step(qb, work, set_idx, record=None):
+    for L in work:
+        if record is not None:
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            e0.record()
+        qb.hadamard_quant(L["x"][set_idx], L["table"], L["khad"], 1.0, out_q=L["q"], out_s=L["s"])
+        if record is not None:
+            e1.record()
+        qb.linear_i4(L["q"], L["s"], L["w"][set_idx], L["sw"][set_idx], out=L["out"])
+        if record is not None:
+            e2.record()
+            record.append((L["name"], e0, e1, e2))
+
+
+def e2e_run(qb, layers, M, dev, steps, warmup, work):
+    """Same step through the module API with HOST buffers: per linear, activations are copied
+    from pinned host memory, pushed through Sequential([HadamardQuantizer|Quantizer], Linear4bit)
+    and the fp16 result is copied back to pinned host memory.  Copies run on their own streams
+    so that transfers of neighbouring linears overlap the kernels."""
+    mods, hx, hout = [], [], []
+    for L in work:
+        lin = qb.nn.Linear4bit(L["K"], L["N"]).to(dev)
+        lin.weight = L["w"][0]
+        lin.weight_scales = L["sw"][0].view(-1, 1)
+        front = qb.nn.HadamardQuantizer(L["K"]) if L["khad"] else qb.nn.Quantizer()
+        mods.append(torch.nn.Sequential(front, lin))
+        hx.append(L["x"][0].cpu().pin_memory())
+        hout.append(torch.empty((M, L["N"]), dtype=torch.float16).pin_memory())
+    h2d_bytes = sum(t.numel() * 2 for t in hx)
+    d2h_bytes = sum(t.numel() * 2 for t in hout)
+    main = torch.cuda.current_stream(dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    dx = [torch.empty_like(L["x"][0]) for L in work]
+
+    def step():
+        start = torch.cuda.Event()
+        start.record(main)
+        s_in.wait_event(start)
+        ready = []
+        with torch.cuda.stream(s_in):
+            for i in range(len(work)):
+                dx[i].copy_(hx[i], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(s_in)
+                ready.append(ev)
+        for i in range(len(work)):
+            main.wait_event(ready[i])
+            out = mods[i](dx[i])
+            done = torch.cuda.Event()
+            done.record(main)
+            s_out.wait_event(done)
+            with torch.cuda.stream(s_out):
+                hout[i].copy_(out, non_blocking=True)
+                out.record_stream(s_out)
+        fin = torch.cuda.Event()
+        fin.record(s_out)
+        main.wait_event(fin)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(main)
+    for _ in range(steps):
+        step()
+    e1.record(main)
+    torch.cuda.synchronize(dev)
+    return e0.elapsed_time(e1) / steps, h2d_bytes, d2h_bytes
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="llama2_7b_prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=0, help="token rows per GPU (default: the workload's)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+
+    from quarot_b200 import synth
+    table_name, default_m = WORKLOADS[args.workload]
+    layers = getattr(synth, table_name)
+    M = args.tokens or default_m
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    n_gpus = max(args.gpus, world)
+    metric = "linear4bit_fused_tops"
+    config = {"workload": args.workload, "tokens_per_gpu": M,
+              "linears": ["%s %d->%d%s" % (n, K, N, " +hadamard" if h else "") for (n, K, N, h) in layers],
+              "sharding": "token rows sharded over ranks, weights replicated, no collective" if n_gpus > 1 else "single GPU",
+              "l2": "activations and weights rotate over 3 buffer sets per step (>1 GB, L2 is 126 MB)"}
+
+    # ------------------------------------------------------------ reference arm (CPU)
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        r = cpu_reference_run(layers, M, args.steps, max(args.warmup, 1))
+        line = {"impl": "reference", "metric": metric, "value": r["value"], "unit": "TOPS", "n_gpus": n_gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step_full"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int4 codes, int32 accumulate (torch CPU int32 matmul)", "data": "synthetic",
+                "config": config, "tokens_per_s": r["tokens_per_s"],
+                "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
+                "e2e": {"value": r["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return 0
+
+    # ------------------------------------------------------------ our arm (GPU)
+    import quarot_b200 as qb
+    from quarot_b200 import _lib
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    nsets = 3
+    work = build_device_workload(layers, M, dev, nsets)
+    for i in range(args.warmup):
+        device_step(qb, work, i % nsets)
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        device_step(qb, work, i % nsets)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    ms_step = e0.elapsed_time(e1) / args.steps
+    if dist is not None:
+        t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item())
+
+    # instrumented pass over the same steps: CUDA events around every kernel of the timed region
+    rec = []
+    for i in range(args.steps):
+        device_step(qb, work, i % nsets, record=rec)
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop() if sampler else None
+    per = {}
+    for (name, a, b, c) in rec:
+        d = per.setdefault(name, {"quant_ms": 0.0, "gemm_ms": 0.0, "n": 0})
+        d["quant_ms"] += a.elapsed_time(b)
+        d["gemm_ms"] += b.elapsed_time(c)
+        d["n"] += 1
+    for d in per.values():
+        d["quant_ms"] /= d["n"]
+        d["gemm_ms"] /= d["n"]
+    status = _lib.kernel_status()
+    if status != 0:
+        raise SystemExit("bench.py: a kernel reported a wait timeout (status %d)" % status)
+
+    total_ops = layer_ops(layers, M) * n_gpus
+    value = total_ops / (ms_step * 1e-3) / 1e12
+    peaks, peak_src = load_peaks()
+    gemm_ms_total = sum(per[n]["gemm_ms"] for (n, _, _, _) in layers)
+    quant_ms_total = sum(per[n]["quant_ms"] for (n, _, _, _) in layers)
+    gemm_ops = layer_ops(layers, M)
+    int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
+    achieved = gemm_ops / (gemm_ms_total * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "kernel": "gemm_i4_kernel (4 launches per step, one per linear)",
+                "achieved": achieved, "peak": int8_peak, "unit": "TOPS", "frac": achieved / int8_peak,
+                "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s): dense int8 runs at twice the "
+                               "bf16 rate on these tensor cores; no int8 figure is in that file" % peak_src,
+                "traffic": None,
+                "frac_of_nominal_4500": achieved / 4500.0}
+    qbytes = sum(bytes_quant(M, K) for (_, K, _, _) in layers)
+    quant_gbs = qbytes / (quant_ms_total * 1e-3) / 1e9
+    line = {"metric": metric, "value": value, "unit": "TOPS", "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "int4 codes widened to int8, int32 accumulate, fp16 out",
+            "data": "synthetic", "config": config,
+            "tokens_per_s": M * n_gpus / (ms_step * 1e-3),
+            "gpu_launches": 2 * len(layers) * args.steps,
+            "roofline": roofline,
+            "quant_kernel": {"bound": "hbm", "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                             "frac": quant_gbs / peaks["hbm_gbs"], "ms_per_step": quant_ms_total},
+            "kernel_ms": per, "clocks": clocks}
+
+    if not args.no_e2e:
+        e2e_ms, h2d, d2h = e2e_run(qb, layers, M, dev, max(3, min(args.steps, 10)), 3, work)
+        if dist is not None:
+            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            e2e_ms = float(t.item())
+        line["e2e"] = {"value": total_ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
+                       "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "api": "torch.nn.Sequential(quarot_b200.nn.[Hadamard]Quantizer, quarot_b200.nn.Linear4bit) "
+                              "with pinned host activations in and host fp16 results out"}
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        r = cpu_reference_run(layers, M, 2, 1, budget_s=12.0)
+        line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -83,7 +83,8 @@ int qr_hadamard_f32(const float* x, float* y, int64_t rows, int64_t n,
  *              was quantised, or NULL
  * Codes are clamp(rint(fp16(y / s)), -8, 7) with the division in fp32, exactly
  * the torch arithmetic of sym_quant (quarot/functional/quantization.py:29-32).
- * A row whose absmax is 0 gets scale 0 and all-zero codes. */
+ * A row whose scale underflows to 0 follows torch's x / 0 arithmetic: zeros give code 0,
+ * positive values 7, negative values -8 (an all-zero row therefore gets all-zero codes). */
 int qr_hadamard_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx,
                          const void* had_k, int K, float clip,
                          uint8_t* q, void* scales, void* y_out, void* stream);

@@ -129,11 +129,12 @@ def hadamard(x, had_k=None, K=1):
     return y.view(*shape_excl_last, n)
 
 
-def hadamard_quant(x, had_k=None, K=0, clip=1.0, return_y=False):
+def hadamard_quant(x, had_k=None, K=0, clip=1.0, return_y=False, out_q=None, out_s=None):
     """Fused [Hadamard ->] per-token scale -> int4 quantise-and-pack.
 
     x fp16 [..., n].  K = 0 skips the transform.  Returns (q uint8 [..., n/2],
-    scales fp16 [rows], y fp16 [..., n] or None).
+    scales fp16 [rows], y fp16 [..., n] or None).  out_q / out_s may supply
+    preallocated contiguous outputs of those shapes.
     """
     assert x.dtype == torch.float16
     x2, shape_excl_last = flatten_last_dim_and_return_shape(x)
@@ -142,13 +143,15 @@ def hadamard_quant(x, had_k=None, K=0, clip=1.0, return_y=False):
     if n % 2:
         raise RuntimeError("hadamard_quant: last dimension must be even")
     with torch.cuda.device(dev):
-        q = torch.empty((rows, n // 2), dtype=torch.uint8, device=dev)
-        s = torch.empty((rows,), dtype=torch.float16, device=dev)
+        q = out_q if out_q is not None else torch.empty((rows, n // 2), dtype=torch.uint8, device=dev)
+        s = out_s if out_s is not None else torch.empty((rows,), dtype=torch.float16, device=dev)
+        if q.numel() != rows * (n // 2) or s.numel() != rows or not q.is_contiguous() or not s.is_contiguous():
+            raise RuntimeError("hadamard_quant: preallocated outputs have the wrong size")
         y = torch.empty((rows, n), dtype=torch.float16, device=dev) if return_y else None
         _lib.check(_lib_c.qr_hadamard_quant_i4(
             x2.data_ptr(), rows, n, n, had_k.data_ptr() if had_k is not None else None, K, float(clip),
             q.data_ptr(), s.data_ptr(), y.data_ptr() if y is not None else None, _stream(dev)), "hadamard_quant")
-    return (q.view(*shape_excl_last, -1), s, y.view(*shape_excl_last, n) if y is not None else None)
+    return (q.view(*shape_excl_last, n // 2), s.view(-1), y.view(*shape_excl_last, n) if y is not None else None)
 
 
 def linear_i4(q_x, scales_x, weight, weight_scales, bias=None, out=None):

@@ -55,6 +55,14 @@ __device__ __forceinline__ uint32_t quant_pair(float q0, float q1) {
   return bits & 0x000F000Fu;
 }
 
+// Codes for a row whose scale is zero: torch evaluates x / 0 = +-inf (or NaN for 0 / 0),
+// so positive values saturate to 7, negative ones to -8 and zeros stay 0.
+__device__ __forceinline__ uint32_t quant_pair_zero_scale(float a, float b) {
+  const uint32_t ca = a > 0.0f ? 7u : (a < 0.0f ? 8u : 0u);
+  const uint32_t cb = b > 0.0f ? 7u : (b < 0.0f ? 8u : 0u);
+  return ca | (cb << 16);
+}
+
 // Correctly rounded fp32 quotient y / s given rcp = RN(1/s): the product y*rcp is
 // refined by two residual (Markstein) steps, which yields the IEEE round-to-nearest
 // quotient for the normal-range operands that occur here (s is a finite non-zero

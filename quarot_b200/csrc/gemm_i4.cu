@@ -29,7 +29,7 @@
 // MMA rows) and the few token rows become operand Q (BN = 16..64); the epilogue then
 // writes the transposed tile.
 //
-// Every mbarrier wait is bounded: after kSpinLimit failed polls the waiting thread
+// Every mbarrier wait is bounded: after about two seconds of polling the waiting thread
 // raises a CTA-wide abort flag and the device status word, every role leaves its
 // loop, tensor memory is released and the kernel returns.
 #include "common.cuh"
@@ -64,13 +64,18 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
-constexpr uint32_t kSpinLimit = 1u << 26;  // polls; several seconds at worst, never reached in a healthy run
+constexpr long long kWaitCycles = 4000000000ll;  // about two seconds of SM clock; never reached in a healthy run
 
-// Bounded wait.  Returns false if the CTA is aborting.
+// Bounded wait.  Returns false if the CTA is aborting (this thread or another one gave up).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 1023u) == 1023u && *abort_flag) return false;
+    if ((i & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) break;
+    }
   }
   *abort_flag = 1;
   atomicExch(status, code);
@@ -169,6 +174,7 @@ struct GemmParams {
   const __half* sP;      // per-row scale of operand P (fp16) or null (MODE_I32)
   const __half* sQ;
   const __half* bias;    // per output channel or null
+  int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int* status;
 };
 
@@ -318,7 +324,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
           if (prow_ok) {
             if (MODE == MODE_I32) {
               int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-              if (qcol0 + CH <= p.rowsQ && (p.ldo & 3) == 0) {
+              if (qcol0 + CH <= p.rowsQ && p.vec_ok) {
 #pragma unroll
                 for (int j = 0; j < CH; j += 4)
                   *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
@@ -330,7 +336,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
               }
             } else {
               __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-              const bool full = (qcol0 + CH <= p.rowsQ) && ((p.ldo & 7) == 0);
+              const bool full = (qcol0 + CH <= p.rowsQ) && p.vec_ok;
               if (full) {
 #pragma unroll
                 for (int j = 0; j < CH; j += 8) {
@@ -510,6 +516,8 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
   p.bias = reinterpret_cast<const __half*>(bias);
+  p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
+             (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
   CUtensorMap tmP, tmQ;
   int rc;
   const int grid_cap = tuning("gemm_grid", 0);

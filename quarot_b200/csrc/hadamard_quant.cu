@@ -312,14 +312,13 @@ hadq_fast_kernel(const HadqParams p) {
       if (yo) reinterpret_cast<uint4*>(yo)[c] = v;
       if (qo) {
         uint32_t packed = 0;
-        if (s != 0.0f) {
-          const __half2* h = reinterpret_cast<const __half2*>(&v);
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            float2 f = __half22float2(h[i]);
-            uint32_t cd = quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp));
-            packed |= ((cd & 0xF) | ((cd >> 12) & 0xF0)) << (8 * i);
-          }
+        for (int i = 0; i < 4; ++i) {
+          float2 f = __half22float2(h[i]);
+          uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
+                                    : quant_pair_zero_scale(f.x, f.y);
+          packed |= ((cd & 0xF) | ((cd >> 12) & 0xF0)) << (8 * i);
         }
         reinterpret_cast<uint32_t*>(qo)[c] = packed;
       }
@@ -398,14 +397,11 @@ hadq_generic_kernel(const HadqParams p) {
       const int nb = (n + 1) >> 1;
       uint8_t* qo = p.q + row * (int64_t)nb;
       for (int j = tid; j < nb; j += nthreads) {
-        uint32_t byte = 0;
-        if (s != 0.0f) {
-          float v0 = cur[2 * j];
-          float v1 = (2 * j + 1 < n) ? cur[2 * j + 1] : 0.0f;
-          uint32_t cd = quant_pair(div_by_scale(v0, s, rcp), div_by_scale(v1, s, rcp));
-          byte = (cd & 0xF) | ((cd >> 12) & 0xF0);
-        }
-        qo[j] = (uint8_t)byte;
+        const float v0 = cur[2 * j];
+        const float v1 = (2 * j + 1 < n) ? cur[2 * j + 1] : 0.0f;
+        const uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(v0, s, rcp), div_by_scale(v1, s, rcp))
+                                        : quant_pair_zero_scale(v0, v1);
+        qo[j] = (uint8_t)((cd & 0xF) | ((cd >> 12) & 0xF0));
       }
     }
     __syncthreads();

@@ -12,7 +12,8 @@ __device__ __forceinline__ uint32_t quant8(const uint4& v, float s, float rcp) {
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     float2 f = __half22float2(h[i]);
-    uint32_t c = quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp));
+    uint32_t c = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
+                             : quant_pair_zero_scale(f.x, f.y);
     // c: code(2i) in bits 3:0, code(2i+1) in bits 19:16  ->  byte i = lo | hi << 4
     out |= ((c & 0xF) | ((c >> 12) & 0xF0)) << (8 * i);
   }
@@ -30,9 +31,7 @@ sym_quant_vec_kernel(const __half* __restrict__ x, const __half* __restrict__ sc
     const int64_t row = i / vec_per_row;
     const float s = __half2float(scale[row]);
     uint4 v = *reinterpret_cast<const uint4*>(x + i * 8);
-    uint32_t packed = 0;
-    if (s != 0.0f) packed = quant8(v, s, __frcp_rn(s));
-    *reinterpret_cast<uint32_t*>(q + i * 4) = packed;
+    *reinterpret_cast<uint32_t*>(q + i * 4) = quant8(v, s, s != 0.0f ? __frcp_rn(s) : 0.0f);
   }
 }
 
@@ -46,15 +45,16 @@ sym_quant_scalar_kernel(const __half* __restrict__ x, const __half* __restrict__
     const int64_t row = i / cols_dst;
     const int64_t c = (i - row * cols_dst) * 2;
     const float s = __half2float(scale[row]);
-    uint32_t byte = 0;
+    const float a = __half2float(x[row * cols + c]);
+    const float b = (c + 1 < cols) ? __half2float(x[row * cols + c + 1]) : 0.0f;
+    uint32_t code;
     if (s != 0.0f) {
       const float rcp = __frcp_rn(s);
-      float a = __half2float(x[row * cols + c]);
-      float b = (c + 1 < cols) ? __half2float(x[row * cols + c + 1]) : 0.0f;
-      uint32_t code = quant_pair(div_by_scale(a, s, rcp), div_by_scale(b, s, rcp));
-      byte = (code & 0xF) | ((code >> 12) & 0xF0);
+      code = quant_pair(div_by_scale(a, s, rcp), div_by_scale(b, s, rcp));
+    } else {
+      code = quant_pair_zero_scale(a, b);
     }
-    q[i] = (uint8_t)byte;
+    q[i] = (uint8_t)((code & 0xF) | ((code >> 12) & 0xF0));
   }
 }
 

