@@ -306,6 +306,9 @@ def main():
     # ------------------------------------------------------------ our arm (GPU)
     import quarot_b200 as qb
     from quarot_b200 import _lib
+    for kv in filter(None, os.environ.get("QR_TUNE", "").split(",")):   # experiments: QR_TUNE=gemm_2sm=0,gemm_pst=6
+        k, v = kv.split("=")
+        _lib.set_tuning(k, int(v))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
     dev = torch.device("cuda", local_rank)

@@ -32,135 +32,13 @@
 // Every mbarrier wait is bounded: after about two seconds of polling the waiting thread
 // raises a CTA-wide abort flag and the device status word, every role leaves its
 // loop, tensor memory is released and the kernel returns.
-#include "common.cuh"
-
-#include <cuda.h>
+#include "tc_ptx.cuh"
 
 #include <map>
 #include <mutex>
 #include <tuple>
 
 namespace qr {
-
-// ------------------------------------------------------------------ PTX
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-
-constexpr long long kWaitCycles = 4000000000ll;  // about two seconds of SM clock; never reached in a healthy run
-
-// Bounded wait.  Returns false if the CTA is aborting (this thread or another one gave up).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(status, code);
-  return false;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-      : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void fence_mbar_init() {
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of 128 B,
-// 8-row groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0,14)
-  d |= (uint64_t)0 << 16;                             // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024u >> 4) << 32;                  // stride byte offset, bits [32,46)
-  d |= (uint64_t)1 << 46;                             // version
-  d |= (uint64_t)2 << 61;                             // layout: SWIZZLE_128B
-  return d;
-}
-
-// Instruction descriptor for kind::i8: signed 8-bit A and B, both K-major, int32 accumulate.
-__host__ __device__ constexpr uint32_t make_idesc_i8(int umma_m, int umma_n) {
-  return (2u << 4)                       // D format: S32
-         | (1u << 7)                     // A format: signed 8-bit
-         | (1u << 10)                    // B format: signed 8-bit
-         | (0u << 15) | (0u << 16)       // A, B K-major
-         | ((uint32_t)(umma_n >> 3) << 17)
-         | ((uint32_t)(umma_m >> 4) << 24);
-}
 
 // ------------------------------------------------------------------ kernel
 enum { MODE_I32 = 0, MODE_F16 = 1 };
@@ -174,6 +52,7 @@ struct GemmParams {
   const __half* sP;      // per-row scale of operand P (fp16) or null (MODE_I32)
   const __half* sQ;
   const __half* bias;    // per output channel or null
+  int sync_mode;         // 2-CTA kernel: bit 0 = plain remote arrives, bit 1 = plain (CTA-scope) waits in the MMA thread
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int* status;
 };
@@ -443,6 +322,272 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   }
 }
 
+// ------------------------------------------------------------------ 2-CTA kernel (cta_group::2)
+// Two CTAs of a cluster share one 256 x 256 output tile.  CTA r loads and widens rows
+// [128 r, 128 r + 128) of BOTH operands; the leader CTA (rank 0) issues
+// tcgen05.mma.cta_group::2 (M = 256, N = 256), which reads A from each CTA's own shared memory
+// and each half of B from the CTA that holds it, so every CTA widens and feeds only half of the
+// weight tile.  Accumulator rows 128 r .. 128 r + 127 live in CTA r's tensor memory and are
+// drained by that CTA's epilogue warps.
+//   full_i  (leader)   <- 8 local + 8 remote widen-warp arrivals (release.cluster)
+//   empty_i (each CTA) <- tcgen05.commit from the leader, one commit per CTA
+//   acc_full (each CTA) <- tcgen05.commit from the leader, one commit per CTA
+//   acc_empty (leader) <- 4 local + 4 remote epilogue-warp arrivals
+// No multicast is used anywhere: TMA loads are CTA-local, commits target one barrier each.
+constexpr int kBN2 = 256;            // N of the pair tile; each CTA holds kBN2 / 2 rows of operand Q
+constexpr int kRows2 = kBM + kBN2 / 2;  // operand rows per CTA per stage (128 P + 128 Q)
+
+template <int PST, int IST>
+struct SmemLayout2 {
+  static constexpr int kI8Stage = kRows2 * 128;
+  static constexpr int kPkStage = kRows2 * kBKBytes;
+  static constexpr int kI8Off = 0;
+  static constexpr int kPkOff = IST * kI8Stage;
+  static constexpr int kBarOff = kPkOff + PST * kPkStage;
+  static constexpr int kNumBars = 2 * PST + 2 * IST + 4;
+  static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
+  static constexpr int kAbortOff = kTmemSlotOff + 8;
+  static constexpr int kTotal = kAbortOff + 8;
+  static constexpr int kDynamic = kTotal + 1024;
+};
+
+template <int PST, int IST, int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
+  using L = SmemLayout2<PST, IST>;
+  constexpr int ACC = 2;
+  extern __shared__ unsigned char smem_dyn[];
+  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
+  unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = (rank == 0);
+
+  const uint32_t bar_base = smem_base + L::kBarOff;
+  auto full_p = [&](int s) { return bar_base + 8u * s; };
+  auto empty_p = [&](int s) { return bar_base + 8u * (PST + s); };
+  auto full_i = [&](int s) { return bar_base + 8u * (2 * PST + s); };
+  auto empty_i = [&](int s) { return bar_base + 8u * (2 * PST + IST + s); };
+  auto acc_full = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + a); };
+  auto acc_empty = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
+  constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps); }
+    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), 2 * kWidenWarps); mbar_init(empty_i(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 2 * kEpiWarps); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_2sm(smem_base + L::kTmemSlotOff, kTmemCols);
+    tmem_relinquish_2sm();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();   // both CTAs' barriers are initialised before any remote arrive
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.tilesP * p.tilesQ;     // pair tiles
+  const int num_kb = (p.K + 127) >> 7;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (own rows only)
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+        const int tp = tile % p.tilesP, tq = tile / p.tilesP;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % PST;
+          const uint32_t ph = (it / PST) & 1;
+          if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
+          mbar_expect_tx(full_p(s), L::kPkStage);
+          const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
+          tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * 2 * kBM + (int)rank * kBM);
+          tma_load_2d(dst + kBM * kBKBytes, &tmQ, full_p(s), kb * kBKBytes, tq * kBN2 + (int)rank * (kBN2 / 2));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+    if (leader && lane == 0) {
+      constexpr uint32_t idesc = make_idesc_i8(2 * kBM, kBN2);
+      const uint32_t peer_empty_i0 = mapa_cluster(empty_i(0), 1);
+      const uint32_t peer_acc_full0 = mapa_cluster(acc_full(0), 1);
+      uint32_t it = 0, tl = 0;
+      bool ok = true;
+      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
+        const int a = tl % ACC;
+        const uint32_t pha = (tl / ACC) & 1;
+        if (!((p.sync_mode & 2) ? mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 12)
+                                 : mbar_wait_cluster(acc_empty(a), pha ^ 1, abort_flag, p.status, 12))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + a * kBN2;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % IST;
+          const uint32_t ph = (it / IST) & 1;
+          if (!((p.sync_mode & 2) ? mbar_wait(full_i(s), ph, abort_flag, p.status, 13)
+                                   : mbar_wait_cluster(full_i(s), ph, abort_flag, p.status, 13))) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + L::kI8Off + s * L::kI8Stage;
+          const uint64_t da = make_kmajor_sw128_desc(a_addr);
+          const uint64_t db = make_kmajor_sw128_desc(a_addr + kBM * 128);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            umma_i8_2sm(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+          umma_commit_2sm(empty_i(s));
+          umma_commit_2sm(peer_empty_i0 + 8u * s);
+        }
+        if (ok) {
+          umma_commit_2sm(acc_full(a));
+          umma_commit_2sm(peer_acc_full0 + 8u * a);
+        }
+      }
+    }
+  } else if (warp < 2 + kEpiWarps) {
+    // ------------------------------------------------------------ epilogue (own 128 accumulator rows)
+    const int q4 = warp & 3;
+    const int prow_in_tile = q4 * 32 + lane;
+    const uint32_t leader_acc_empty0 = mapa_cluster(acc_empty(0), 0);
+    uint32_t tl = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
+      const int tp = tile % p.tilesP, tq = tile / p.tilesP;
+      const int a = tl % ACC;
+      const uint32_t pha = (tl / ACC) & 1;
+      if (!mbar_wait(acc_full(a), pha, abort_flag, p.status, 14)) { ok = false; break; }
+      tc_fence_after();
+      const int prow = tp * 2 * kBM + (int)rank * kBM + prow_in_tile;
+      const bool prow_ok = prow < p.rowsP;
+      float sp = 0.0f;
+      if (MODE == MODE_F16 && prow_ok) sp = __half2float(p.sP[prow]);
+#pragma unroll 1
+      for (int c0 = 0; c0 < kBN2; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0), r);
+        tmem_ld_wait();
+        if (c0 + 32 >= kBN2) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_acc_empty0 + 8u * a);
+            else mbar_arrive_cluster(leader_acc_empty0 + 8u * a);
+          }
+        }
+        const int qcol0 = tq * kBN2 + c0;
+        if (prow_ok) {
+          if (MODE == MODE_I32) {
+            int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
+            if (qcol0 + 32 <= p.rowsQ && p.vec_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
+                                                            (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (qcol0 + j < p.rowsQ) o[j] = (int32_t)r[j] >> 8;
+            }
+          } else {
+            __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
+            if ((qcol0 + 32 <= p.rowsQ) && p.vec_ok) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __half2* h = reinterpret_cast<__half2*>(&pk);
+                const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + j));
+                const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 sc = __half22float2(sqh[e]);
+                  h[e] = __floats2half2_rn((float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x),
+                                           (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y));
+                }
+                if (p.bias) {
+                  const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + j));
+                  const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
+                }
+                *reinterpret_cast<uint4*>(o + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (qcol0 + j < p.rowsQ) {
+                  const float sc = __half2float(p.sQ[qcol0 + j]);
+                  __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sp * sc));
+                  if (p.bias) v = __hadd(v, p.bias[qcol0 + j]);
+                  o[j] = v;
+                }
+              }
+            }
+          }
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ widen int4 -> int8 (own rows)
+    const int wt = threadIdx.x - 32 * (2 + kEpiWarps);
+    constexpr int kChunks = kRows2 * 4;
+    constexpr int kWThreads = 32 * kWidenWarps;
+    const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
+    uint32_t it = 0;
+    bool ok = true;
+    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int sp_ = it % PST, si = it % IST;
+        const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
+        if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
+        if (!mbar_wait(empty_i(si), phi ^ 1, abort_flag, p.status, 16)) { ok = false; break; }
+        tc_fence_after();
+        const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
+        unsigned char* i8 = smem_gen + L::kI8Off + si * L::kI8Stage;
+#pragma unroll
+        for (int c = wt; c < kChunks; c += kWThreads) {
+          const int row = c >> 2, cc = c & 3;
+          const uint4 w = *reinterpret_cast<const uint4*>(pk + c * 16);
+          uint4 lo, hi;
+          lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;
+          lo.y = (w.y << 4) & 0xF0F0F0F0u; hi.y = w.y & 0xF0F0F0F0u;
+          lo.z = (w.z << 4) & 0xF0F0F0F0u; hi.z = w.z & 0xF0F0F0F0u;
+          lo.w = (w.w << 4) & 0xF0F0F0F0u; hi.w = w.w & 0xF0F0F0F0u;
+          unsigned char* drow = i8 + row * 128;
+          const int sw = row & 7;
+          *reinterpret_cast<uint4*>(drow + (((2 * cc) ^ sw) << 4)) = lo;
+          *reinterpret_cast<uint4*>(drow + (((2 * cc + 1) ^ sw) << 4)) = hi;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * si);
+          else mbar_arrive_cluster(leader_full_i0 + 8u * si);
+          mbar_arrive(empty_p(sp_));
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  __syncwarp();
+  cluster_sync_all();   // the peer may still read this CTA's shared memory or arrive on its barriers
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------ host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -496,6 +641,41 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
   return QR_OK;
 }
 
+template <int PST, int IST, int MODE>
+static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
+  using L = SmemLayout2<PST, IST>;
+  static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
+  auto kern = gemm_i4_2sm_kernel<PST, IST, MODE>;
+  static thread_local int max_clusters[64] = {0};
+  int dev = 0;
+  QR_CUDA(cudaGetDevice(&dev));
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kDynamic;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int nclusters = (dev < 64) ? max_clusters[dev] : 0;
+  if (nclusters == 0) {
+    QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
+    cfg.gridDim = dim3(2 * (num_sms() / 2));
+    QR_CUDA(cudaOccupancyMaxActiveClusters(&nclusters, kern, &cfg));
+    if (nclusters < 1) return fail(QR_EUNSUPPORTED, "2-CTA GEMM: no cluster of 2 CTAs fits on this device");
+    if (dev < 64) max_clusters[dev] = nclusters;
+  }
+  int clusters = p.tilesP * p.tilesQ;
+  if (clusters > nclusters) clusters = nclusters;
+  if (grid_cap > 0 && clusters > grid_cap) clusters = grid_cap;
+  cfg.gridDim = dim3(2 * clusters);
+  QR_CUDA(cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, p));
+  return QR_OK;
+}
+
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st) {
@@ -515,12 +695,22 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   const bool swap = M <= swap_max_m;
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
+  p.sync_mode = tuning("gemm_sync", 3);
   p.bias = reinterpret_cast<const __half*>(bias);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
   CUtensorMap tmP, tmQ;
   int rc;
   const int grid_cap = tuning("gemm_grid", 0);
+  if (!swap && M > kBM && tuning("gemm_2sm", 1) != 0) {
+    p.rowsP = (int)M; p.rowsQ = (int)N;
+    p.tilesP = (int)((M + 2 * kBM - 1) / (2 * kBM)); p.tilesQ = (int)((N + kBN2 - 1) / kBN2);
+    p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
+    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
+    if ((rc = make_packed_map(&tmQ, B, N, K / 2, kBN2 / 2))) return rc;
+    if (tuning("gemm_pst", 4) == 6) return launch_gemm_2sm<6, 4, MODE>(tmP, tmQ, p, grid_cap, st);
+    return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, p, grid_cap, st);
+  }
   if (!swap) {
     int bn = tuning("gemm_bn", 256);
     if (bn != 256 && bn != 128 && bn != 64) bn = 256;

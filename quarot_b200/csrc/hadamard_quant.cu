@@ -48,6 +48,7 @@ struct HadqParams {
   __half* scales;
   void* y_out;
   int do_quant;
+  int top_bits;       // Walsh-only kernel: 2 when the two top index bits of a work item belong to the transform
 };
 
 __device__ __forceinline__ int phys(int i) { return i ^ (((i >> 5) & 7) << 2); }
@@ -77,31 +78,39 @@ __device__ __forceinline__ float absmax8(const uint4& v) {
   return fmaxf(f.x, f.y);
 }
 
-// One radix-2^R pass over index bits [b, b+R), b >= 5, in place in buf32.
-// When `final`, results are scaled, rounded to fp16 and written to buf16 instead.
+// Radix-2^R pass over index bits [5, 5+R), in place in the swizzled fp32 row buffer.
+// Lanes map to address bits 0..4, so every access is conflict free; the swizzle term of
+// element j reduces to the compile-time constant (j & 7) << 2.
 template <int R>
-__device__ __forceinline__ void scalar_pass(float* buf32, __half* buf16, int n, int b, bool final,
-                                            float scale, float& amax, int tid, int nthreads) {
+__device__ __forceinline__ void pass_b5(float* buf32, int n, int tid, int nthreads) {
   constexpr int N = 1 << R;
   const int groups = n >> R;
   for (int gid = tid; gid < groups; gid += nthreads) {
-    const int low = gid & ((1 << b) - 1);
-    const int base = low | ((gid >> b) << (b + R));
+    const int base = (gid & 31) | ((gid >> 5) << (5 + R));
+    const int pb = phys(base);
     float v[N];
 #pragma unroll
-    for (int j = 0; j < N; ++j) v[j] = buf32[phys(base + (j << b))];
+    for (int j = 0; j < N; ++j) v[j] = buf32[(pb ^ ((j & 7) << 2)) + (j << 5)];
     fwht_regs<N>(v);
-    if (!final) {
 #pragma unroll
-      for (int j = 0; j < N; ++j) buf32[phys(base + (j << b))] = v[j];
-    } else {
+    for (int j = 0; j < N; ++j) buf32[(pb ^ ((j & 7) << 2)) + (j << 5)] = v[j];
+  }
+}
+
+// Radix-2^R pass over index bits [b, b+R) with b >= 8: the swizzle term is the same for all j.
+template <int R>
+__device__ __forceinline__ void pass_hi(float* buf32, int n, int b, int tid, int nthreads) {
+  constexpr int N = 1 << R;
+  const int groups = n >> R;
+  for (int gid = tid; gid < groups; gid += nthreads) {
+    const int base = (gid & ((1 << b) - 1)) | ((gid >> b) << (b + R));
+    const int pb = phys(base);
+    float v[N];
 #pragma unroll
-      for (int j = 0; j < N; ++j) {
-        __half y = __float2half_rn(v[j] * scale);
-        buf16[base + (j << b)] = y;
-        amax = fmaxf(amax, fabsf(__half2float(y)));
-      }
-    }
+    for (int j = 0; j < N; ++j) v[j] = buf32[pb + (j << b)];
+    fwht_regs<N>(v);
+#pragma unroll
+    for (int j = 0; j < N; ++j) buf32[pb + (j << b)] = v[j];
   }
 }
 
@@ -118,9 +127,109 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
                : "r"(addr));
 }
 
-// KT = number of 16-wide k tiles of the dense factor (0 when K <= 1).
+// 32 fp16 values (16 half2) -> 16 packed bytes, with torch's division arithmetic.
+__device__ __forceinline__ uint4 quant32(const __half2 (&h)[16], float s, float rcp) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t packed = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __half22float2(h[4 * i + e]);
+      const uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
+                                      : quant_pair_zero_scale(f.x, f.y);
+      packed |= ((cd | (cd >> 12)) & 0xFFu) << (8 * e);
+    }
+    w[i] = packed;
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+__device__ __forceinline__ uint32_t quant8_u4(const uint4& v, float s, float rcp) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+  uint32_t packed = 0;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float2 f = __half22float2(h[e]);
+    const uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
+                                    : quant_pair_zero_scale(f.x, f.y);
+    packed |= ((cd | (cd >> 12)) & 0xFFu) << (8 * e);
+  }
+  return packed;
+}
+
+// Row absmax across the CTA: warp shuffle, one slot per warp, one barrier.
+__device__ __forceinline__ float block_absmax(float amax, float* red, int lane, int warp, int nwarps) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  float a = (lane < nwarps) ? red[lane] : 0.0f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+  return a;
+}
+
+__device__ __forceinline__ float scale_from_absmax(float a, float clip, __half* out) {
+  const __half s7 = __float2half_rn(__fdiv_rn(a, 7.0f));
+  const __half sh = __float2half_rn(__half2float(s7) * clip);
+  if (out) *out = sh;
+  return __half2float(sh);
+}
+
+// Quantise-only kernel (no transform): the row never touches shared memory.  Thread t owns the
+// 16-byte chunks t, t + T, t + 2T, t + 3T of the row (coalesced), keeps them in registers across
+// the row-wide absmax reduction and stores 4 packed bytes per chunk.  The next row's loads are
+// issued before the current row is reduced.
+__global__ void __launch_bounds__(1024)
+quant_rows_kernel(const HadqParams p) {
+  __shared__ float red[2][32];
+  const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
+  const int nchunks = p.n >> 3;
+  uint4 cur[4], nxt[4];
+  int64_t row = blockIdx.x;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  if (row < p.rows) {
+    const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + row * p.ldx);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xr + tid + j * T) : zero;
+  }
+  int parity = 0;
+  for (; row < p.rows; row += gridDim.x, parity ^= 1) {
+    const int64_t nrow = row + gridDim.x;
+    if (nrow < p.rows) {
+      const uint4* xn = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + nrow * p.ldx);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) nxt[j] = (tid + j * T < nchunks) ? __ldg(xn + tid + j * T) : zero;
+    }
+    float amax = fmaxf(fmaxf(absmax8(cur[0]), absmax8(cur[1])), fmaxf(absmax8(cur[2]), absmax8(cur[3])));
+    const float a = block_absmax(amax, red[parity], lane, warp, nwarps);
+    const float s = scale_from_absmax(a, p.clip, tid == 0 ? p.scales + row : nullptr);
+    const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+    uint32_t* qo = reinterpret_cast<uint32_t*>(p.q + row * (int64_t)(p.n >> 1));
+    uint4* yo = p.y_out ? reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.y_out) + row * (int64_t)p.n) : nullptr;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = tid + j * T;
+      if (c < nchunks) {
+        qo[c] = quant8_u4(cur[j], s, rcp);
+        if (yo) yo[c] = cur[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+  }
+}
+
+// KT = number of 16-wide k tiles of the dense factor (0 when K == 1).  One thread per group of
+// 32 consecutive outputs; blockDim.x >= n / 32 (rounded up to whole warps).
+// Largest CTA each instantiation is compiled for (bounds the registers per thread).
+__host__ __device__ constexpr int hadq_max_threads(int KT) {
+  return KT == 0 ? 512 : KT <= 2 ? 1024 : KT <= 4 ? 512 : KT == 7 ? 448 : KT == 9 ? 576 : KT == 10 ? 640 : 384;
+}
+
 template <int KT>
-__global__ void __launch_bounds__(512, 1)
+__global__ void __launch_bounds__(hadq_max_threads(KT))
 hadq_fast_kernel(const HadqParams p) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x;
@@ -131,20 +240,19 @@ hadq_fast_kernel(const HadqParams p) {
   const int n = p.n;
   const int m = p.m;
   const int K = p.K;
+  const int ngroups = n >> 5;
 
-  // shared memory carve-up: [fp32 row buffer][fp16 row / raw staging][reduction scratch]
-  const int buf32_bytes = (K >= 1) ? n * 4 : 0;
-  const int pitch = m + 8;  // halfs; staging pitch for the dense-factor operand
-  const int raw_halfs = (KT > 0) ? KT * 16 * pitch : 0;
-  const int buf16_halfs = raw_halfs > n ? raw_halfs : n;
+  // shared memory: [fp32 row buffer (swizzled)][staging for the dense-factor operand][reduction slots]
+  const int pitch = m + 8;  // halfs
+  const int raw_bytes = (KT > 0) ? ((KT * 16 * pitch * 2 + 15) & ~15) : 0;
   float* buf32 = reinterpret_cast<float*>(smem_raw);
-  __half* buf16 = reinterpret_cast<__half*>(smem_raw + buf32_bytes);
-  float* red = reinterpret_cast<float*>(smem_raw + buf32_bytes + ((buf16_halfs * 2 + 15) & ~15));
+  __half* raw = reinterpret_cast<__half*>(smem_raw + (size_t)n * 4);
+  float* red = reinterpret_cast<float*>(smem_raw + (size_t)n * 4 + raw_bytes);
 
-  // dense-factor fragments: warp w owns 16 output rows (M tile w % MT) for good
+  // dense-factor fragments: warp w owns 16 output rows (M tile w % MT) for the lifetime of the CTA
   constexpr int KTT = KT > 0 ? KT : 1;
-  uint32_t afrag[KTT][4];
   constexpr int MT = KT > 0 ? KT : 1;
+  uint32_t afrag[KTT][4];
   const int my_mt = (KT > 0) ? warp % MT : 0;
   if (KT > 0) {
     const int g = lane >> 2, t = lane & 3;
@@ -162,168 +270,157 @@ hadq_fast_kernel(const HadqParams p) {
     }
   }
 
-  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x) {
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
     const __half* xr = reinterpret_cast<const __half*>(p.x) + row * p.ldx;
-    float amax = 0.0f;
+    int scalar_bits = p.wbits - 5;   // index bits left for the shared-memory passes
 
-    if (K == 0) {
+    if (KT > 0) {
+      // ---- stage 0: raw row -> padded staging, zero the padding rows
+      const int vec_per_k = m >> 3;
       for (int c = tid; c < (n >> 3); c += nthreads) {
-        uint4 v = __ldg(reinterpret_cast<const uint4*>(xr) + c);
-        reinterpret_cast<uint4*>(buf16)[c] = v;
-        amax = fmaxf(amax, absmax8(v));
+        const int k = c / vec_per_k;
+        const int mm = (c - k * vec_per_k) << 3;
+        *reinterpret_cast<uint4*>(raw + k * pitch + mm) = __ldg(reinterpret_cast<const uint4*>(xr) + c);
       }
-    } else {
-      const bool low_is_final = (p.wbits == 5);
-      if (KT > 0) {
-        // ---- stage 0: raw row -> padded staging, zero the padding rows
-        const int vec_per_k = m >> 3;
-        for (int c = tid; c < (n >> 3); c += nthreads) {
-          const int k = c / vec_per_k;
-          const int mm = (c - k * vec_per_k) << 3;
-          uint4 v = __ldg(reinterpret_cast<const uint4*>(xr) + c);
-          *reinterpret_cast<uint4*>(buf16 + k * pitch + mm) = v;
-        }
-        const int pad_vecs = (KT * 16 - K) * vec_per_k;
-        for (int c = tid; c < pad_vecs; c += nthreads) {
-          const int k = K + c / vec_per_k;
-          const int mm = (c % vec_per_k) << 3;
-          *reinterpret_cast<uint4*>(buf16 + k * pitch + mm) = make_uint4(0, 0, 0, 0);
-        }
-        __syncthreads();
-        // ---- stage 1: D = hadK . X on tensor cores, 64 columns per unit
-        const int nchunks = m >> 6;
-        const int warps_per_mt = nwarps / MT;
-        if (warp < warps_per_mt * MT) {
-          const int g = lane >> 2, t = lane & 3;
-          // ldmatrix lane address: matrix j = lane / 8 -> (k half j & 1, n tile j >> 1), row lane % 8
-          const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
-          const int lcol = (lane >> 4) * 8;
-          for (int ch = warp / MT; ch < nchunks; ch += warps_per_mt) {
-            float acc[8][4];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
-#pragma unroll
-            for (int kt = 0; kt < KTT; ++kt) {
-#pragma unroll
-              for (int np = 0; np < 4; ++np) {
-                uint32_t b[4];
-                const __half* src = buf16 + (kt * 16 + lrow) * pitch + ch * 64 + np * 16 + lcol;
-                ldmatrix_x4_trans(b, smem_u32(src));
-                mma_16816(acc[2 * np], afrag[kt], b[0], b[1]);
-                mma_16816(acc[2 * np + 1], afrag[kt], b[2], b[3]);
-              }
-            }
-            const int r0 = my_mt * 16 + g;
-#pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-              const int col = ch * 64 + nt * 8 + 2 * t;
-              if (r0 < K)
-                *reinterpret_cast<float2*>(buf32 + phys(r0 * m + col)) = make_float2(acc[nt][0], acc[nt][1]);
-              if (r0 + 8 < K)
-                *reinterpret_cast<float2*>(buf32 + phys((r0 + 8) * m + col)) = make_float2(acc[nt][2], acc[nt][3]);
-            }
-          }
-        }
-        __syncthreads();  // staging (aliased by buf16) is dead from here on
+      const int pad_vecs = (KT * 16 - K) * vec_per_k;
+      for (int c = tid; c < pad_vecs; c += nthreads) {
+        const int k = K + c / vec_per_k;
+        const int mm = (c % vec_per_k) << 3;
+        *reinterpret_cast<uint4*>(raw + k * pitch + mm) = make_uint4(0, 0, 0, 0);
       }
-      // ---- low pass: index bits 0..4
-      for (int G = tid; G < (n >> 5); G += nthreads) {
-        float v[32];
-        if (KT > 0) {
+      __syncthreads();
+      // ---- stage 1: D = hadK . X on tensor cores, 64 columns per unit
+      const int nchunks = m >> 6;
+      const int warps_per_mt = nwarps / MT;
+      if (warp < warps_per_mt * MT) {
+        const int g = lane >> 2, t = lane & 3;
+        const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int lcol = (lane >> 4) * 8;
+        for (int ch = warp / MT; ch < nchunks; ch += warps_per_mt) {
+          float acc[8][4];
 #pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            float4 f = *reinterpret_cast<const float4*>(buf32 + G * 32 + ((s ^ (G & 7)) << 2));
-            v[4 * s] = f.x; v[4 * s + 1] = f.y; v[4 * s + 2] = f.z; v[4 * s + 3] = f.w;
-          }
-        } else {
+          for (int i = 0; i < 8; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            uint4 u = __ldg(reinterpret_cast<const uint4*>(xr) + G * 4 + s);
-            const __half2* h = reinterpret_cast<const __half2*>(&u);
+          for (int kt = 0; kt < KTT; ++kt) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float2 f = __half22float2(h[e]);
-              v[8 * s + 2 * e] = f.x;
-              v[8 * s + 2 * e + 1] = f.y;
+            for (int np = 0; np < 4; ++np) {
+              uint32_t b[4];
+              ldmatrix_x4_trans(b, smem_u32(raw + (kt * 16 + lrow) * pitch + ch * 64 + np * 16 + lcol));
+              mma_16816(acc[2 * np], afrag[kt], b[0], b[1]);
+              mma_16816(acc[2 * np + 1], afrag[kt], b[2], b[3]);
             }
           }
-        }
-        fwht_regs<32>(v);
-        if (!low_is_final) {
+          const int r0 = my_mt * 16 + g;
 #pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            *reinterpret_cast<float4*>(buf32 + G * 32 + ((s ^ (G & 7)) << 2)) =
-                make_float4(v[4 * s], v[4 * s + 1], v[4 * s + 2], v[4 * s + 3]);
-          }
-        } else {
-#pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            uint4 u;
-            __half2* h = reinterpret_cast<__half2*>(&u);
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              h[e] = __floats2half2_rn(v[8 * s + 2 * e] * p.scale, v[8 * s + 2 * e + 1] * p.scale);
-            reinterpret_cast<uint4*>(buf16)[G * 4 + s] = u;
-            amax = fmaxf(amax, absmax8(u));
+          for (int nt = 0; nt < 8; ++nt) {
+            const int col = ch * 64 + nt * 8 + 2 * t;
+            if (r0 < K)
+              *reinterpret_cast<float2*>(buf32 + phys(r0 * m + col)) = make_float2(acc[nt][0], acc[nt][1]);
+            if (r0 + 8 < K)
+              *reinterpret_cast<float2*>(buf32 + phys((r0 + 8) * m + col)) = make_float2(acc[nt][2], acc[nt][3]);
           }
         }
       }
-      // ---- scalar passes: index bits 5 .. wbits-1, at most four per pass, balanced
-      int rem = p.wbits - 5;
-      int b = 5;
-      while (rem > 0) {
-        const int npass = (rem + 3) >> 2;
-        const int r = (rem + npass - 1) / npass;
-        const bool fin = (rem == r);
-        __syncthreads();
-        if (r == 4) scalar_pass<4>(buf32, buf16, n, b, fin, p.scale, amax, tid, nthreads);
-        else if (r == 3) scalar_pass<3>(buf32, buf16, n, b, fin, p.scale, amax, tid, nthreads);
-        else if (r == 2) scalar_pass<2>(buf32, buf16, n, b, fin, p.scale, amax, tid, nthreads);
-        else scalar_pass<1>(buf32, buf16, n, b, fin, p.scale, amax, tid, nthreads);
-        b += r;
-        rem -= r;
+    } else {
+      // ---- stage A (Walsh only): coalesced 128-bit loads; thread t owns chunks t + j * n/32, i.e. the
+      //      two top index bits are local, and transforms them when they belong to the transform
+      const bool top2 = (p.top_bits == 2);
+      if (top2) scalar_bits -= 2;
+      if (tid < ngroups) {
+        float v[4][8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 u = __ldg(reinterpret_cast<const uint4*>(xr) + tid + j * ngroups);
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(h[e]);
+            v[j][2 * e] = f.x;
+            v[j][2 * e + 1] = f.y;
+          }
+        }
+        if (top2) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float t0 = v[0][e] + v[1][e], t1 = v[0][e] - v[1][e];
+            const float t2 = v[2][e] + v[3][e], t3 = v[2][e] - v[3][e];
+            v[0][e] = t0 + t2; v[1][e] = t1 + t3; v[2][e] = t0 - t2; v[3][e] = t1 - t3;
+          }
+        }
+        const int sw = ((tid >> 2) & 7) << 2;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int i0 = 8 * tid + j * (n >> 2);
+          *reinterpret_cast<float4*>(buf32 + (i0 ^ sw)) = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+          *reinterpret_cast<float4*>(buf32 + ((i0 + 4) ^ sw)) = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+        }
       }
     }
 
-    // ---- per-row scale
-    float s = 0.0f;
+    // ---- scalar passes over index bits 5 .. 5 + scalar_bits - 1
+    if (scalar_bits > 0) {
+      int r1 = scalar_bits <= 5 ? scalar_bits : (scalar_bits + 1) / 2;
+      if (r1 > 4 && scalar_bits > 5) r1 = 4;
+      __syncthreads();
+      switch (r1) {
+        case 1: pass_b5<1>(buf32, n, tid, nthreads); break;
+        case 2: pass_b5<2>(buf32, n, tid, nthreads); break;
+        case 3: pass_b5<3>(buf32, n, tid, nthreads); break;
+        case 4: pass_b5<4>(buf32, n, tid, nthreads); break;
+        default: pass_b5<5>(buf32, n, tid, nthreads); break;
+      }
+      int b = 5 + r1;
+      int rem = scalar_bits - r1;
+      while (rem > 0) {   // b >= 8 here because r1 >= 3 whenever a second pass exists
+        const int r = rem > 4 ? (rem + 1) / 2 : rem;
+        __syncthreads();
+        switch (r) {
+          case 1: pass_hi<1>(buf32, n, b, tid, nthreads); break;
+          case 2: pass_hi<2>(buf32, n, b, tid, nthreads); break;
+          case 3: pass_hi<3>(buf32, n, b, tid, nthreads); break;
+          default: pass_hi<4>(buf32, n, b, tid, nthreads); break;
+        }
+        b += r < 4 ? r : 4;
+        rem -= r < 4 ? r : 4;
+      }
+    }
+    __syncthreads();
+
+    // ---- final pass: index bits 0..4 in registers; thread t ends with outputs [32 t, 32 t + 32)
+    __half2 h[16];
+    float amax = 0.0f;
+    if (tid < ngroups) {
+      float v[32];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const float4 f = *reinterpret_cast<const float4*>(buf32 + tid * 32 + ((s ^ (tid & 7)) << 2));
+        v[4 * s] = f.x; v[4 * s + 1] = f.y; v[4 * s + 2] = f.z; v[4 * s + 3] = f.w;
+      }
+      fwht_regs<32>(v);
+      __half2 mx = __float2half2_rn(0.0f);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        h[e] = __floats2half2_rn(v[2 * e] * p.scale, v[2 * e + 1] * p.scale);
+        mx = __hmax2(mx, __habs2(h[e]));
+      }
+      const float2 mf = __half22float2(mx);
+      amax = fmaxf(mf.x, mf.y);
+      if (p.y_out) {
+        uint4* yo = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.y_out) + row * (int64_t)n + tid * 32);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) yo[s] = *reinterpret_cast<const uint4*>(&h[4 * s]);
+      }
+    }
     if (p.do_quant) {
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-      if (lane == 0) red[warp] = amax;
-      __syncthreads();
-      float a = (lane < nwarps) ? red[lane] : 0.0f;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
-      const __half s7 = __float2half_rn(__fdiv_rn(a, 7.0f));
-      const __half sh = __float2half_rn(__half2float(s7) * p.clip);
-      s = __half2float(sh);
-      if (tid == 0) p.scales[row] = sh;
+      const float a = block_absmax(amax, red + 32 * parity, lane, warp, nwarps);
+      const float s = scale_from_absmax(a, p.clip, tid == 0 ? p.scales + row : nullptr);
+      const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+      if (tid < ngroups)
+        *reinterpret_cast<uint4*>(p.q + row * (int64_t)(n >> 1) + tid * 16) = quant32(h, s, rcp);
     } else {
-      __syncthreads();
+      __syncthreads();   // the row buffer is rewritten by the next row
     }
-
-    // ---- quantise / emit
-    const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
-    __half* yo = p.y_out ? reinterpret_cast<__half*>(p.y_out) + row * (int64_t)n : nullptr;
-    uint8_t* qo = p.do_quant ? p.q + row * (int64_t)(n >> 1) : nullptr;
-    for (int c = tid; c < (n >> 3); c += nthreads) {
-      uint4 v = reinterpret_cast<const uint4*>(buf16)[c];
-      if (yo) reinterpret_cast<uint4*>(yo)[c] = v;
-      if (qo) {
-        uint32_t packed = 0;
-        const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float2 f = __half22float2(h[i]);
-          uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
-                                    : quant_pair_zero_scale(f.x, f.y);
-          packed |= ((cd & 0xF) | ((cd >> 12) & 0xF0)) << (8 * i);
-        }
-        reinterpret_cast<uint32_t*>(qo)[c] = packed;
-      }
-    }
-    __syncthreads();  // buffers are reused by the next row
   }
 }
 
@@ -411,25 +508,27 @@ hadq_generic_kernel(const HadqParams p) {
 // ---------------------------------------------------------------- dispatch
 static int kt_for(int K) { return K > 1 ? (K + 15) / 16 : 0; }
 
+static int persistent_grid(int64_t rows, int threads, size_t smem) {
+  int per_sm = (int)(227 * 1024 / (smem + 1024));
+  const int by_threads = 2048 / threads;
+  if (per_sm > by_threads) per_sm = by_threads;
+  if (per_sm > 16) per_sm = 16;
+  if (per_sm < 1) per_sm = 1;
+  int64_t grid = (int64_t)num_sms() * per_sm;
+  if (grid > rows) grid = rows;
+  return (int)grid;
+}
+
 template <int KT>
 static int launch_fast(const HadqParams& p, int threads, size_t smem, cudaStream_t st) {
   static thread_local size_t configured[64] = {0};
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && configured[dev] < smem) {
+  if (dev >= 64 || configured[dev] < smem) {
     QR_CUDA(cudaFuncSetAttribute(hadq_fast_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    configured[dev] = smem;
-  } else if (dev >= 64) {
-    QR_CUDA(cudaFuncSetAttribute(hadq_fast_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = smem;
   }
-  // persistent grid: as many CTAs as fit at once
-  int per_sm = (int)(227 * 1024 / (smem + 1024));
-  int by_threads = 2048 / threads;
-  if (per_sm > by_threads) per_sm = by_threads;
-  if (per_sm < 1) per_sm = 1;
-  int64_t grid = (int64_t)num_sms() * per_sm;
-  if (grid > p.rows) grid = p.rows;
-  hadq_fast_kernel<KT><<<(int)grid, threads, smem, st>>>(p);
+  hadq_fast_kernel<KT><<<persistent_grid(p.rows, threads, smem), threads, smem, st>>>(p);
   QR_LAUNCH_CHECK("hadq_fast_kernel");
   return QR_OK;
 }
@@ -487,36 +586,36 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
   p.scale = (K >= 1) ? (float)(1.0 / sqrt((double)n)) : 1.0f;
   p.clip = clip; p.q = q; p.scales = reinterpret_cast<__half*>(scales); p.y_out = y_out; p.do_quant = do_quant;
 
+  p.top_bits = 0;
   const int forced = tuning("hadq_path", 0);  // 1 = always generic (for A/B checks)
-  bool fast = (elem_size == 2) && forced != 1 && aligned16(x) && (ldx % 8 == 0) && (n % 8 == 0) &&
-              (!y_out || aligned16(y_out)) && (!do_quant || (((uintptr_t)q & 3) == 0));
+  const bool base_ok = (elem_size == 2) && forced != 1 && aligned16(x) && (ldx % 8 == 0) && (n % 8 == 0) &&
+                       (!y_out || aligned16(y_out)) && (!do_quant || aligned16(q)) && n <= 32768;
+  if (base_ok && K == 0 && do_quant && n >= 64) {
+    int threads = ((n / 8 + 3) / 4 + 31) / 32 * 32;
+    quant_rows_kernel<<<persistent_grid(rows, threads, 1024), threads, 0, st>>>(p);
+    QR_LAUNCH_CHECK("quant_rows_kernel");
+    return QR_OK;
+  }
+  bool fast = base_ok && K >= 1 && (n % 32 == 0) && (!do_quant || (n % 32 == 0));
   if (fast) {
-    if (K == 0) fast = (n >= 256) && ((size_t)n * 2 <= 200 * 1024);
-    else if (K == 1) fast = (n >= 1024);
+    if (K == 1) { fast = (n >= 1024); p.top_bits = 2; }
     else fast = (m >= 64);
   }
   // Walsh-only with short rows and no quantisation: batch 1024/n consecutive rows per work item
-  if (!fast && elem_size == 2 && forced != 1 && K == 1 && !do_quant && n >= 32 && n < 1024 && ldx == n &&
-      aligned16(x) && aligned16(y_out)) {
+  if (!fast && base_ok && K == 1 && !do_quant && n >= 32 && n < 1024 && ldx == n) {
     const int per = 1024 / n;
     if (rows % per == 0) {
-      p.n = 1024; p.rows = rows / per; p.ldx = 1024; p.m = n; fast = true;
+      p.n = 1024; p.rows = rows / per; p.ldx = 1024; p.m = n; p.top_bits = 0; fast = true;
     }
   }
   if (fast) {
     const int KT = kt_for(K);
     const int pitch = p.m + 8;
-    const size_t raw = KT ? (size_t)KT * 16 * pitch * 2 : 0;
-    size_t b16 = (size_t)p.n * 2;
-    if (raw > b16) b16 = raw;
-    b16 = (b16 + 15) & ~(size_t)15;
-    const size_t smem = (K >= 1 ? (size_t)p.n * 4 : 0) + b16 + 32 * 4;
-    if (smem <= 227 * 1024) {
-      int threads = (p.n / 32 + 31) / 32 * 32;
-      if (K == 0) threads = (p.n / 8 + 31) / 32 * 32;
-      if (threads < 64) threads = 64;
-      if (threads > 512) threads = 512;
-      if (KT > 0 && threads < KT * 32) threads = KT * 32;
+    const size_t raw = KT ? (((size_t)KT * 16 * pitch * 2 + 15) & ~(size_t)15) : 0;
+    const size_t smem = (size_t)p.n * 4 + raw + 256;
+    int threads = (p.n / 32 + 31) / 32 * 32;
+    if (KT > 0 && threads < KT * 32) threads = KT * 32;
+    if (smem <= 227 * 1024 && threads <= hadq_max_threads(KT)) {
       switch (KT) {
         case 0: return launch_fast<0>(p, threads, smem, st);
         case 1: return launch_fast<1>(p, threads, smem, st);
@@ -531,7 +630,7 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
       }
     }
     // restore the unbatched description
-    p.n = n; p.rows = rows; p.ldx = ldx; p.m = m;
+    p.n = n; p.rows = rows; p.ldx = ldx; p.m = m; p.top_bits = 0;
   }
   if (elem_size == 2) return launch_generic<__half>(p, st);
   return launch_generic<float>(p, st);

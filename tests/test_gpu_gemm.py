@@ -63,17 +63,34 @@ def test_matmul_leading_dims_and_errors():
         qb.matmul(a.to(DEV).transpose(0, 1), b.to(DEV))
 
 
-@pytest.mark.parametrize("tiles", ["bn128", "bn64", "pst3", "grid3"])
+TILE_CONFIGS = {
+    "2sm_grid3": {"gemm_grid": 3},
+    "2sm_pst6": {"gemm_pst": 6},
+    "1sm_bn256": {"gemm_2sm": 0},
+    "1sm_bn128": {"gemm_2sm": 0, "gemm_bn": 128},
+    "1sm_bn64": {"gemm_2sm": 0, "gemm_bn": 64},
+    "1sm_pst3": {"gemm_2sm": 0, "gemm_pst": 3},
+    "1sm_grid3": {"gemm_2sm": 0, "gemm_grid": 3},
+}
+TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0}
+
+
+@pytest.mark.parametrize("tiles", sorted(TILE_CONFIGS))
 def test_matmul_other_tile_configs_agree(tiles):
-    key, val = {"bn128": ("gemm_bn", 128), "bn64": ("gemm_bn", 64), "pst3": ("gemm_pst", 3), "grid3": ("gemm_grid", 3)}[tiles]
     a, b = _rand_packed(300, 2048, 1), _rand_packed(1000, 2048, 2)
     want = O.matmul_i4(a, b)
-    _lib.set_tuning(key, val)
+    sx = (torch.rand(300) * 0.5 + 0.05).half()
+    sw = (torch.rand(1000) * 0.015 + 0.005).half()
+    for k, v in TILE_CONFIGS[tiles].items():
+        _lib.set_tuning(k, v)
     try:
         c = qb.matmul(a.to(DEV), b.to(DEV)).cpu()
+        o = qb.linear_i4(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV)).cpu()
     finally:
-        _lib.set_tuning(key, 256 if key == "gemm_bn" else (4 if key == "gemm_pst" else 0))
+        for k, v in TILE_DEFAULTS.items():
+            _lib.set_tuning(k, v)
     assert torch.equal(c, want)
+    assert torch.equal(o, O.sym_dequant_fp32(want, sx, sw).half())
     assert _lib.kernel_status() == 0
 
 
