@@ -52,7 +52,8 @@ struct GemmParams {
   const __half* sP;      // per-row scale of operand P (fp16) or null (MODE_I32)
   const __half* sQ;
   const __half* bias;    // per output channel or null
-  int sync_mode;         // 2-CTA kernel: bit 0 = plain remote arrives, bit 1 = plain (CTA-scope) waits in the MMA thread
+  int sync_mode;         // 2-CTA kernel: bit 0 = plain remote arrives, bit 1 = plain (CTA-scope) waits in the MMA thread,
+                         // bit 2 = one commit delivered to both CTAs instead of one commit per CTA
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int* status;
 };
@@ -329,11 +330,12 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 // and each half of B from the CTA that holds it, so every CTA widens and feeds only half of the
 // weight tile.  Accumulator rows 128 r .. 128 r + 127 live in CTA r's tensor memory and are
 // drained by that CTA's epilogue warps.
-//   full_i  (leader)   <- 8 local + 8 remote widen-warp arrivals (release.cluster)
+//   full_i  (leader)   <- 4 local + 4 remote widen-warp arrivals (the group that owns the stage)
 //   empty_i (each CTA) <- tcgen05.commit from the leader, one commit per CTA
 //   acc_full (each CTA) <- tcgen05.commit from the leader, one commit per CTA
 //   acc_empty (leader) <- 4 local + 4 remote epilogue-warp arrivals
-// No multicast is used anywhere: TMA loads are CTA-local, commits target one barrier each.
+// TMA loads are CTA-local (no multicast of data); the MMA-completion signal is one commit
+// delivered to the same barrier in both CTAs.
 constexpr int kBN2 = 256;            // N of the pair tile; each CTA holds kBN2 / 2 rows of operand Q
 constexpr int kRows2 = kBM + kBN2 / 2;  // operand rows per CTA per stage (128 P + 128 Q)
 
@@ -377,8 +379,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps); }
-    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), 2 * kWidenWarps); mbar_init(empty_i(s), 1); }
+    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps / 2); }
+    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), kWidenWarps); mbar_init(empty_i(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 2 * kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -443,12 +445,20 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
             umma_i8_2sm(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
-          umma_commit_2sm(empty_i(s));
-          umma_commit_2sm(peer_empty_i0 + 8u * s);
+          if (p.sync_mode & 4) {
+            umma_commit_2sm_mc(empty_i(s), 3);
+          } else {
+            umma_commit_2sm(empty_i(s));
+            umma_commit_2sm(peer_empty_i0 + 8u * s);
+          }
         }
         if (ok) {
-          umma_commit_2sm(acc_full(a));
-          umma_commit_2sm(peer_acc_full0 + 8u * a);
+          if (p.sync_mode & 4) {
+            umma_commit_2sm_mc(acc_full(a), 3);
+          } else {
+            umma_commit_2sm(acc_full(a));
+            umma_commit_2sm(peer_acc_full0 + 8u * a);
+          }
         }
       }
     }
@@ -536,30 +546,41 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     }
   } else {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
+    // Two groups of four warps take alternate k-blocks, so that a group has two MMA periods per
+    // stage.  Packed data is read into registers before the int8 slot is waited for, which keeps
+    // the shared-memory read off the slot-reuse critical path.
     const int wt = threadIdx.x - 32 * (2 + kEpiWarps);
-    constexpr int kChunks = kRows2 * 4;
-    constexpr int kWThreads = 32 * kWidenWarps;
+    const int group = (wt >> 5) & 1;
+    const int gt = (wt & 31) | ((wt >> 6) << 5);        // 0 .. 127 inside the group
+    constexpr int kChunks = kRows2 * 4;                 // 1024 packed 16-byte chunks per stage
+    constexpr int kGThreads = 32 * kWidenWarps / 2;     // 128
+    constexpr int kPer = kChunks / kGThreads;           // 8 chunks per thread
+    static_assert(PST % 2 == 0 && IST % 2 == 0, "alternating groups need even ring sizes");
     const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
     uint32_t it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((int)(it & 1u) != group) continue;
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
+        const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
+        uint4 w[kPer];
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) w[j] = *reinterpret_cast<const uint4*>(pk + (gt + j * kGThreads) * 16);
         if (!mbar_wait(empty_i(si), phi ^ 1, abort_flag, p.status, 16)) { ok = false; break; }
         tc_fence_after();
-        const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
         unsigned char* i8 = smem_gen + L::kI8Off + si * L::kI8Stage;
 #pragma unroll
-        for (int c = wt; c < kChunks; c += kWThreads) {
+        for (int j = 0; j < kPer; ++j) {
+          const int c = gt + j * kGThreads;
           const int row = c >> 2, cc = c & 3;
-          const uint4 w = *reinterpret_cast<const uint4*>(pk + c * 16);
           uint4 lo, hi;
-          lo.x = (w.x << 4) & 0xF0F0F0F0u; hi.x = w.x & 0xF0F0F0F0u;
-          lo.y = (w.y << 4) & 0xF0F0F0F0u; hi.y = w.y & 0xF0F0F0F0u;
-          lo.z = (w.z << 4) & 0xF0F0F0F0u; hi.z = w.z & 0xF0F0F0F0u;
-          lo.w = (w.w << 4) & 0xF0F0F0F0u; hi.w = w.w & 0xF0F0F0F0u;
+          lo.x = (w[j].x << 4) & 0xF0F0F0F0u; hi.x = w[j].x & 0xF0F0F0F0u;
+          lo.y = (w[j].y << 4) & 0xF0F0F0F0u; hi.y = w[j].y & 0xF0F0F0F0u;
+          lo.z = (w[j].z << 4) & 0xF0F0F0F0u; hi.z = w[j].z & 0xF0F0F0F0u;
+          lo.w = (w[j].w << 4) & 0xF0F0F0F0u; hi.w = w[j].w & 0xF0F0F0F0u;
           unsigned char* drow = i8 + row * 128;
           const int sw = row & 7;
           *reinterpret_cast<uint4*>(drow + (((2 * cc) ^ sw) << 4)) = lo;
@@ -570,6 +591,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         if (lane == 0) {
           if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * si);
           else mbar_arrive_cluster(leader_full_i0 + 8u * si);
+          // the staging slot is released only here: the stores above consumed every loaded register,
+          // so the loads have certainly completed
           mbar_arrive(empty_p(sp_));
         }
       }
@@ -695,7 +718,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   const bool swap = M <= swap_max_m;
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
-  p.sync_mode = tuning("gemm_sync", 3);
+  p.sync_mode = tuning("gemm_sync", 7);
   p.bias = reinterpret_cast<const __half*>(bias);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
