@@ -32,6 +32,10 @@
 
 namespace qr {
 
+// tensor-core kernel for n = 64 K (hadamard_tc.cu); QR_EUNSUPPORTED means "not my shape"
+int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k, float clip, uint8_t* q,
+                   void* scales, void* y_out, int do_quant, cudaStream_t st);
+
 struct HadqParams {
   const void* x;
   int64_t ldx;        // elements between work items
@@ -595,6 +599,10 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
     quant_rows_kernel<<<persistent_grid(rows, threads, 1024), threads, 0, st>>>(p);
     QR_LAUNCH_CHECK("quant_rows_kernel");
     return QR_OK;
+  }
+  if (base_ok && K > 1 && m == 64 && ldx == n && tuning("hadq_tc", 1) != 0) {
+    const int rc = launch_hadq_tc(x, rows, n, K, had_k, clip, q, scales, y_out, do_quant, st);
+    if (rc != QR_EUNSUPPORTED) return rc;
   }
   bool fast = base_ok && K >= 1 && (n % 32 == 0) && (!do_quant || (n % 32 == 0));
   if (fast) {

@@ -64,15 +64,17 @@ def test_matmul_leading_dims_and_errors():
 
 
 TILE_CONFIGS = {
-    "2sm_grid3": {"gemm_grid": 3},
-    "2sm_pst6": {"gemm_pst": 6},
+    "2sm_ts": {"gemm_ts": 1},
+    "2sm_ts_grid3": {"gemm_ts": 1, "gemm_grid": 3},
+    "2sm_ss_grid3": {"gemm_grid": 3},
+    "2sm_ss_pst6": {"gemm_pst": 6},
     "1sm_bn256": {"gemm_2sm": 0},
     "1sm_bn128": {"gemm_2sm": 0, "gemm_bn": 128},
     "1sm_bn64": {"gemm_2sm": 0, "gemm_bn": 64},
     "1sm_pst3": {"gemm_2sm": 0, "gemm_pst": 3},
     "1sm_grid3": {"gemm_2sm": 0, "gemm_grid": 3},
 }
-TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0}
+TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_ts": 0, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0}
 
 
 @pytest.mark.parametrize("tiles", sorted(TILE_CONFIGS))
