@@ -21,6 +21,7 @@
 #ifndef QUAROT_B200_H
 #define QUAROT_B200_H
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -120,6 +121,19 @@ int qr_sym_dequant_i32_f16(const int32_t* q, const void* scale_row, const void* 
 int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
                      const void* bias, int64_t M, int64_t N, int64_t K,
                      void* out, int64_t ldo, void* stream);
+
+/* Decode-sized M (M <= 64) is bound by streaming the weights; with few output tiles a single pass
+ * leaves most SMs idle, so the K loop of every tile can be split over several CTAs that meet in a
+ * caller-provided scratch buffer (int32 partial tiles + one arrival counter per tile; the split that
+ * arrives last reduces, nobody waits).  qr_linear_workspace_bytes returns the bytes needed for a
+ * shape (0 when no split would be used).  The workspace must be 256-byte aligned device memory that
+ * was zeroed once before its first use (the kernel leaves the counters at zero) and must not be
+ * shared by launches that may overlap on the GPU.  Same result as qr_linear_i4_f16, bit for bit.
+ * No upstream counterpart: upstream runs one CUTLASS GEMM without split-K (quarot/kernels/gemm.cu:16-41). */
+size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
+int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
+                        const void* bias, int64_t M, int64_t N, int64_t K,
+                        void* out, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -1,6 +1,6 @@
 """ctypes binding of libquarot_b200.so (the C-ABI declared in include/quarot_b200.h).
 
-The library is built in-tree by ``python -m quarot_b200.build``.  There is no
+The library is built in-tree by ``python quarot_b200/build.py``.  There is no
 fallback: if it is missing, importing this module raises.
 """
 import ctypes
@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libquarot_b200.so")
 
 if not os.path.exists(LIB_PATH):
     raise ImportError(
-        "quarot_b200: %s not found -- build it with `python -m quarot_b200.build` "
+        "quarot_b200: %s not found -- build it with `python quarot_b200/build.py` "
         "(needs nvcc with sm_100a support); there is no non-CUDA fallback" % LIB_PATH)
 
 lib = ctypes.CDLL(LIB_PATH)
@@ -31,9 +31,14 @@ SIGNATURES = {
     "qr_matmul_i4_i32": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),
     "qr_sym_dequant_i32_f16": (_int, [_vp, _vp, _vp, _i64, _i64, _vp, _vp]),
     "qr_linear_i4_f16": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "qr_linear_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
+    "qr_linear_i4_f16_ws": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, ctypes.c_size_t, _vp]),
 }
 
 for _name, (_res, _args) in SIGNATURES.items():
+    if not hasattr(lib, _name):
+        raise ImportError("quarot_b200: %s does not export %s -- it is stale, rebuild it with "
+                          "`python quarot_b200/build.py`" % (LIB_PATH, _name))
     _fn = getattr(lib, _name)
     _fn.restype = _res
     _fn.argtypes = _args

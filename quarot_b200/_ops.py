@@ -154,11 +154,27 @@ def hadamard_quant(x, had_k=None, K=0, clip=1.0, return_y=False, out_q=None, out
     return (q.view(*shape_excl_last, n // 2), s.view(-1), y.view(*shape_excl_last, n) if y is not None else None)
 
 
-def linear_i4(q_x, scales_x, weight, weight_scales, bias=None, out=None):
+_WORKSPACES = {}
+
+
+def _workspace(dev, nbytes):
+    """Per-(device, stream) zero-initialised scratch for the split-K decode path, grown on demand.
+    Launches on one stream are ordered, so they can share it; different streams get their own."""
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def linear_i4(q_x, scales_x, weight, weight_scales, bias=None, out=None, use_workspace=True):
     """Fused Linear4bit forward: int4 GEMM with the dequantisation in the epilogue.
 
     q_x uint8 [..., K/2], scales_x fp16 (any shape with one entry per row),
     weight uint8 [N, K/2], weight_scales fp16 [N] or [N, 1].  Returns fp16 [..., N].
+    For decode-sized inputs (at most 64 rows) the K loop is split over more CTAs through a cached
+    scratch buffer (`use_workspace=False` selects the single-pass kernel; results are identical).
     """
     assert q_x.shape[-1] % 32 == 0, "A.shape[-1]: {} must be multiplication of 32".format(q_x.shape[-1])
     assert scales_x.dtype == weight_scales.dtype == torch.float16
@@ -179,7 +195,15 @@ def linear_i4(q_x, scales_x, weight, weight_scales, bias=None, out=None):
         if out is None:
             out = torch.empty((M, N), dtype=torch.float16, device=dev)
         ldo = out.stride(0) if M > 1 else max(out.stride(0), N)
-        _lib.check(_lib_c.qr_linear_i4_f16(A.data_ptr(), sx.data_ptr(), weight.data_ptr(), sw.data_ptr(),
-                                           bias.data_ptr() if bias is not None else None, M, N, K,
-                                           out.data_ptr(), ldo, _stream(dev)), "linear_i4")
+        ws_bytes = _lib_c.qr_linear_workspace_bytes(M, N, K) if use_workspace else 0
+        if ws_bytes:
+            ws = _workspace(dev, ws_bytes)
+            rc = _lib_c.qr_linear_i4_f16_ws(A.data_ptr(), sx.data_ptr(), weight.data_ptr(), sw.data_ptr(),
+                                            bias.data_ptr() if bias is not None else None, M, N, K,
+                                            out.data_ptr(), ldo, ws.data_ptr(), ws.numel(), _stream(dev))
+        else:
+            rc = _lib_c.qr_linear_i4_f16(A.data_ptr(), sx.data_ptr(), weight.data_ptr(), sw.data_ptr(),
+                                         bias.data_ptr() if bias is not None else None, M, N, K,
+                                         out.data_ptr(), ldo, _stream(dev))
+        _lib.check(rc, "linear_i4")
     return out.view(*A_shape_excl_last, N) if out.is_contiguous() else out

@@ -1,6 +1,6 @@
 """Builds libquarot_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m quarot_b200.build [--force] [--verbose]
+    python quarot_b200/build.py [--force] [--verbose]
 
 The library has no dependency on torch or Python; it links the static CUDA
 runtime and resolves the one driver entry point it needs

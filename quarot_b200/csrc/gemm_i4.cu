@@ -54,6 +54,9 @@ struct GemmParams {
   const __half* bias;    // per output channel or null
   int sync_mode;         // 2-CTA kernel: bit 0 = plain remote arrives, bit 1 = plain (CTA-scope) waits in the MMA thread,
                          // bit 2 = one commit delivered to both CTAs instead of one commit per CTA
+  int splits;            // 1-CTA kernel: k splits per tile (1 = none); > 1 needs the scratch buffers below
+  int32_t* ws_partial;   // [tiles][splits][BN][128] int32 partial tiles
+  int* ws_counter;       // [tiles] arrival counters, zero before and after every launch
   int debug;             // timing experiments only (results are wrong when non-zero)
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int* status;
@@ -99,6 +102,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   auto acc_empty = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + 2 + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
+  volatile int* last_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff + 4);
 
   constexpr uint32_t kTmemCols = (ACC * BN) < 32 ? 32 : (ACC * BN);
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
@@ -119,17 +123,23 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int num_tiles = p.tilesP * p.tilesQ;
-  const int num_kb = (p.K + 127) >> 7;
+  // A work item is (tile, k split): split sp of a tile covers k-blocks [kb0, kb1).  With splits == 1 this
+  // is the plain tile loop; with splits > 1 (decode-sized M) partial tiles meet in a scratch buffer.
+  const int splits = p.splits;
+  const int num_tiles = p.tilesP * p.tilesQ * splits;
+  const int num_kb_all = (p.K + 127) >> 7;
+  auto kb_begin = [&](int w) { return (int)(((long long)(w % splits) * num_kb_all) / splits); };
+  auto kb_end = [&](int w) { return (int)(((long long)(w % splits + 1) * num_kb_all) / splits); };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
+        const int tile = w / splits;
         const int tp = tile % p.tilesP, tq = tile / p.tilesP;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_begin(w); kb < kb_end(w); ++kb, ++it) {
           const int s = it % PST;
           const uint32_t ph = (it / PST) & 1;
           if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
@@ -146,13 +156,14 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
       constexpr uint32_t idesc = make_idesc_i8(kBM, BN);
       uint32_t it = 0, tl = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
+      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tl) {
         const int a = tl % ACC;
         const uint32_t pha = (tl / ACC) & 1;
         if (!mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        const int kb0 = kb_begin(w);
+        for (int kb = kb0; kb < kb_end(w); ++kb, ++it) {
           const int s = it % IST;
           const uint32_t ph = (it / IST) & 1;
           if (!mbar_wait(full_i(s), ph, abort_flag, p.status, 3)) { ok = false; break; }
@@ -163,7 +174,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
-            umma_i8(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+            umma_i8(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
           }
           umma_commit(empty_i(s));
         }
@@ -176,7 +187,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const int prow_in_tile = q4 * 32 + lane; // accumulator row owned by this thread
     uint32_t tl = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
+    for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tl) {
+      const int tile = w / splits, sp_idx = w % splits;
       const int tp = tile % p.tilesP, tq = tile / p.tilesP;
       const int a = tl % ACC;
       const uint32_t pha = (tl / ACC) & 1;
@@ -200,6 +212,13 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
           if (lane == 0) mbar_arrive(acc_empty(a));
         }
         const int qcol0 = tq * BN + c0;
+        if (splits > 1) {
+          // partial tile -> scratch, column-major so that the 32 lanes of a warp store 128 contiguous bytes
+          int32_t* part = p.ws_partial + ((size_t)(tile * splits + sp_idx) * BN + c0) * kBM + prow_in_tile;
+#pragma unroll
+          for (int j = 0; j < CH; ++j) part[(size_t)j * kBM] = (int32_t)r[j] >> 8;
+          continue;
+        }
         if (!SWAP) {
           // thread owns output row `prow` (a token), columns qcol0.. (output channels)
           if (prow_ok) {
@@ -273,6 +292,47 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
           }
         }
       }
+      if (splits > 1) {
+        // The split that arrives last at the tile's counter adds up all partial tiles and writes the output;
+        // nobody waits for anybody.  The counter is left at zero for the next launch.
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"r"(32 * kEpiWarps) : "memory");
+        if (threadIdx.x == 32 * 2) *last_flag = (atomicAdd(p.ws_counter + tile, 1) == splits - 1) ? 1 : 0;
+        asm volatile("bar.sync 1, %0;" ::"r"(32 * kEpiWarps) : "memory");
+        if (*last_flag) {
+          __threadfence();
+          if (prow_ok) {
+            for (int j = 0; j < BN; ++j) {
+              const int col = tq * BN + j;
+              if (col >= p.rowsQ) break;
+              int32_t acc = 0;
+              for (int s2 = 0; s2 < splits; ++s2)
+                acc += __ldcg(p.ws_partial + ((size_t)(tile * splits + s2) * BN + j) * kBM + prow_in_tile);
+              if (SWAP) {
+                if (MODE == MODE_I32) {
+                  reinterpret_cast<int32_t*>(p.out)[(int64_t)col * p.ldo + prow] = acc;
+                } else {
+                  const float sc = __half2float(__ldg(p.sQ + col));
+                  __half v = __float2half_rn((float)acc * (sc * sp));
+                  if (p.bias) v = __hadd(v, p.bias[prow]);
+                  reinterpret_cast<__half*>(p.out)[(int64_t)col * p.ldo + prow] = v;
+                }
+              } else {
+                if (MODE == MODE_I32) {
+                  reinterpret_cast<int32_t*>(p.out)[(int64_t)prow * p.ldo + col] = acc;
+                } else {
+                  const float sc = __half2float(__ldg(p.sQ + col));
+                  __half v = __float2half_rn((float)acc * (sp * sc));
+                  if (p.bias) v = __hadd(v, p.bias[col]);
+                  reinterpret_cast<__half*>(p.out)[(int64_t)prow * p.ldo + col] = v;
+                }
+              }
+            }
+          }
+          if (threadIdx.x == 32 * 2) p.ws_counter[tile] = 0;
+        }
+        asm volatile("bar.sync 1, %0;" ::"r"(32 * kEpiWarps) : "memory");
+      }
     }
   } else {
     // ------------------------------------------------------------ widen int4 -> int8
@@ -281,8 +341,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     constexpr int kWThreads = 32 * kWidenWarps;
     uint32_t it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+    for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
+      for (int kb = kb_begin(w); kb < kb_end(w); ++kb, ++it) {
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 5)) { ok = false; break; }
@@ -1069,7 +1129,7 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
     QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
     if (dev < 64) configured[dev] = true;
   }
-  int grid = p.tilesP * p.tilesQ;
+  int grid = p.tilesP * p.tilesQ * p.splits;
   int cap = grid_cap > 0 ? grid_cap : num_sms();
   if (grid > cap) grid = cap;
   kern<<<grid, kThreads, L::kDynamic, st>>>(tmP, tmQ, p);
@@ -1129,9 +1189,24 @@ static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clus
   return QR_OK;
 }
 
+// Number of k splits the decode path would use for (M, N, K) and the scratch bytes that needs
+// (arrival counters, padded to 256 bytes, followed by the int32 partial tiles).
+static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes) {
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  const int tiles = (int)((N + kBM - 1) / kBM) * (int)((M + bn - 1) / bn);
+  const int num_kb = (int)((K + 127) / 128);
+  int splits = num_sms() / (tiles > 0 ? tiles : 1);
+  if (splits > 8) splits = 8;
+  if (splits > num_kb / 4) splits = num_kb / 4;
+  if (splits < 1) splits = 1;
+  if (bytes) *bytes = splits > 1 ? (((size_t)tiles * 4 + 255) & ~(size_t)255) + (size_t)tiles * splits * bn * kBM * 4 : 0;
+  return splits;
+}
+
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
-                    void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st) {
+                    void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
+                    void* ws = nullptr, size_t ws_bytes = 0) {
   if (M < 0 || N < 0 || K < 0) return fail(QR_EINVAL, "%s: negative size", who);
   if (M == 0 || N == 0) return QR_OK;
   if (!A || !B || !out) return fail(QR_EINVAL, "%s: null pointer", who);
@@ -1148,6 +1223,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   const bool swap = M <= swap_max_m;
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
+  p.splits = 1; p.ws_partial = nullptr; p.ws_counter = nullptr;
   p.sync_mode = tuning("gemm_sync", 7);
   p.debug = tuning("gemm_debug", 0);
   p.bias = reinterpret_cast<const __half*>(bias);
@@ -1186,8 +1262,21 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
     if (bn == 128) return launch_gemm<128, 4, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
     return launch_gemm<64, 6, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
   }
-  // decode-sized M: weights fill the MMA rows, tokens are the MMA columns
+  // decode-sized M: weights fill the MMA rows, tokens are the MMA columns; with a scratch buffer the K
+  // loop of a tile is split over several CTAs so that all SMs stream weights
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  if (ws && tuning("gemm_splitk", 1) != 0) {
+    size_t need = 0;
+    const int splits = decode_splits(M, N, K, &need);
+    if (splits > 1) {
+      if (ws_bytes < need) return fail(QR_EINVAL, "%s: workspace of %zu bytes is too small, %zu needed", who, ws_bytes, need);
+      if (((uintptr_t)ws & 255) != 0) return fail(QR_EALIGN, "%s: workspace must be 256-byte aligned", who);
+      const size_t tiles = (size_t)((N + kBM - 1) / kBM) * (size_t)((M + bn - 1) / bn);
+      p.splits = splits;
+      p.ws_counter = reinterpret_cast<int*>(ws);
+      p.ws_partial = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(ws) + ((tiles * 4 + 255) & ~(size_t)255));
+    }
+  }
   p.rowsP = (int)N; p.rowsQ = (int)M;
   p.tilesP = (int)((N + kBM - 1) / kBM); p.tilesQ = (int)((M + bn - 1) / bn);
   p.sP = reinterpret_cast<const __half*>(sB); p.sQ = reinterpret_cast<const __half*>(sA);
@@ -1211,6 +1300,20 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
                      int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16", A, B, M, N, K, out, ldo, sA, sB, bias,
                                     (cudaStream_t)stream);
+}
+
+size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || M > qr::tuning("gemm_swap_max_m", 64)) return 0;
+  size_t bytes = 0;
+  qr::decode_splits(M, N, K, &bytes);
+  return bytes;
+}
+
+int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
+                        int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_ws", A, B, M, N, K, out, ldo, sA, sB, bias,
+                                    (cudaStream_t)stream, workspace, workspace_bytes);
 }
 
 }  // extern "C"

@@ -11,7 +11,8 @@
 // the epilogue warps reads its 64 accumulators with tcgen05.ld, runs the 6 butterfly stages in
 // registers (no shuffles, no shared memory), scales, rounds to fp16, joins the row-wide absmax
 // (per-warp slots published through a bounded mbarrier), quantises with torch's division arithmetic and stores 32 packed bytes.
-// Accumulators are double buffered so the MMAs of row i+1 overlap the epilogue of row i.
+// Accumulators are double buffered and two sets of epilogue warps take alternate token rows, so the
+// MMAs of row i+1 and the epilogue of row i-1 overlap the epilogue of row i.
 //
 // All mbarrier waits are bounded (see tc_ptx.cuh); on a timeout the CTA sets the device status
 // word, leaves its loops, frees tensor memory and returns.
@@ -38,8 +39,8 @@ struct HadqTcParams {
   int* status;
 };
 
-constexpr int kTcEpiWarps = 8;
-constexpr int kTcThreads = 32 * (2 + kTcEpiWarps);
+constexpr int kTcEpiWarps = 8;        // epilogue warps per set; two sets take alternate token rows
+constexpr int kTcThreads = 32 * (2 + 2 * kTcEpiWarps);
 constexpr int kTcNB = 3;              // token-row buffers
 constexpr int kTcNumBars = 2 * kTcNB + 4 + 2;   // full_b, empty_b, acc_full[2], acc_empty[2], red_bar[2]
 
@@ -187,14 +188,15 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
     }
   } else {
     // ------------------------------------------------------------ epilogue: thread = output row k'
-    const int ew = warp - 2;
+    const int set = (warp - 2) >> 3;           // set 0 drains accumulator buffer 0 (even rows), set 1 buffer 1
+    const int ew = (warp - 2) & 7;
     const int mt = ew >> 2, q4 = warp & 3;
     const int kprime = mt * 128 + q4 * 32 + lane;
     const bool warp_active = (mt * 128 + q4 * 32) < p.K && mt < p.MT;
     const bool active = kprime < p.K && mt < p.MT;
     const int n = p.K * 64;
-    uint32_t i = 0;
-    for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, ++i) {
+    uint32_t i = set;
+    for (int64_t row = blockIdx.x + (int64_t)set * gridDim.x; row < p.rows; row += 2 * (int64_t)gridDim.x, i += 2) {
       const int a = i & 1;
       __half2 h[32];
       float amax = 0.0f;

@@ -192,3 +192,36 @@ def test_full_size_config0_properties():
     # determinism: a second run is bitwise identical
     assert torch.equal(qb.linear_i4(q, s, w.to(DEV), sw.to(DEV)), out)
     assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 4096, 4096), (32, 4096, 11008), (64, 4096, 4096),
+                                   (17, 1000, 2048), (64, 512, 28672)])
+def test_decode_split_k_matches_single_pass(M, N, K):
+    """Decode-sized M: the K loop is split over CTAs through the scratch buffer; same bits as one pass."""
+    g = torch.Generator().manual_seed(M + K)
+    a, w = _rand_packed(M, K, 11), _rand_packed(N, K, 12)
+    sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand(N, generator=g) * 0.015 + 0.005).half()
+    bias = (torch.randn(N, generator=g) * 0.5).half()
+    need = _lib.lib.qr_linear_workspace_bytes(M, N, K)
+    assert need > 0
+    ad, wd, sxd, swd, bd = a.to(DEV), w.to(DEV), sx.to(DEV), sw.to(DEV), bias.to(DEV)
+    one = qb.linear_i4(ad, sxd, wd, swd, bd, use_workspace=False)
+    for _ in range(3):   # repeated launches: the arrival counters must come back to zero
+        split = qb.linear_i4(ad, sxd, wd, swd, bd)
+        assert torch.equal(split, one)
+    ref = O.sym_dequant_fp32(O.matmul_i4(a, w), sx, sw).half() + bias
+    assert torch.equal(one.cpu(), ref)
+    assert _lib.kernel_status() == 0
+
+
+def test_workspace_argument_errors():
+    a, w = _rand_packed(8, 4096, 1).to(DEV), _rand_packed(4096, 4096, 2).to(DEV)
+    sx, sw = torch.ones(8, device=DEV).half(), torch.ones(4096, device=DEV).half()
+    out = torch.empty(8, 4096, device=DEV, dtype=torch.float16)
+    need = _lib.lib.qr_linear_workspace_bytes(8, 4096, 4096)
+    small = torch.zeros(256, dtype=torch.uint8, device=DEV)
+    rc = _lib.lib.qr_linear_i4_f16_ws(a.data_ptr(), sx.data_ptr(), w.data_ptr(), sw.data_ptr(), None, 8, 4096, 4096,
+                                      out.data_ptr(), 4096, small.data_ptr(), small.numel(), None)
+    assert rc == -1 and "workspace" in _lib.last_error() and need > 256
+    assert _lib.lib.qr_linear_workspace_bytes(2048, 4096, 4096) == 0     # prefill shapes never split
