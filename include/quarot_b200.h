@@ -135,6 +135,31 @@ int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, cons
                         const void* bias, int64_t M, int64_t N, int64_t K,
                         void* out, int64_t ldo, void* workspace, size_t workspace_bytes, void* stream);
 
+/* qr_linear_i4_f16 for callers that cannot allocate device memory.  This entry point has no
+ * counterpart in the upstream project.
+ *
+ * Who needs it: a host that gave all of its device memory to one arena at start-up (an inference
+ * server with a fixed HBM budget, a framework whose caching allocator owns the rest of the card)
+ * has nowhere to take the split-K workspace of qr_linear_i4_f16_ws from -- a late cudaMalloc can
+ * fail there, and where it succeeds it synchronises the whole device in the middle of the decode
+ * loop; a plain C caller in that loop may not own an allocator at all.  For them the scratch of the
+ * decode kernel lives inside the library image: a fixed array of 4 MiB + 4 KiB in device memory, held by
+ * every GPU that loads the library until the process exits.
+ *
+ * Same arguments and the same result, bit for bit, as qr_linear_i4_f16.  The call allocates nothing
+ * (no cudaMalloc / cudaFree, no allocating library routine).  Limits and rules:
+ *   - shapes whose split-K scratch (qr_linear_workspace_bytes) exceeds that size are refused with
+ *     QR_EUNSUPPORTED and a message; the LLaMA-2 7B and 70B decode shapes up to M = 64 fit;
+ *   - the first call on each device looks up the array's device address (once per device, with
+ *     that device current); make that first call before any stream capture begins;
+ *   - all calls share the one array and find the previous call's contents in it; the entry point
+ *     clears the arrival counters it relies on at the start of every call, but two calls that may
+ *     overlap on the GPU (different streams without an ordering between them) race on the array --
+ *     order them, or give one of them its own workspace through qr_linear_i4_f16_ws. */
+int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
+                            const void* bias, int64_t M, int64_t N, int64_t K,
+                            void* out, int64_t ldo, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

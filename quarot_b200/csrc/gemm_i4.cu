@@ -1191,7 +1191,7 @@ static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clus
 
 // Number of k splits the decode path would use for (M, N, K) and the scratch bytes that needs
 // (arrival counters, padded to 256 bytes, followed by the int32 partial tiles).
-static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes) {
+static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t* counter_bytes = nullptr) {
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int tiles = (int)((N + kBM - 1) / kBM) * (int)((M + bn - 1) / bn);
   const int num_kb = (int)((K + 127) / 128);
@@ -1200,6 +1200,7 @@ static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes) {
   if (splits > num_kb / 4) splits = num_kb / 4;
   if (splits < 1) splits = 1;
   if (bytes) *bytes = splits > 1 ? (((size_t)tiles * 4 + 255) & ~(size_t)255) + (size_t)tiles * splits * bn * kBM * 4 : 0;
+  if (counter_bytes) *counter_bytes = ((size_t)tiles * 4 + 255) & ~(size_t)255;
   return splits;
 }
 
@@ -1307,6 +1308,52 @@ size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   size_t bytes = 0;
   qr::decode_splits(M, N, K, &bytes);
   return bytes;
+}
+
+// ---- scratch that lives inside the library image (see qr_linear_i4_f16_static) -----------------
+// In host code the array's name is only a handle: the device address has to be asked for with
+// cudaGetSymbolAddress, once per device and with that device current.
+namespace qr {
+constexpr size_t kStaticScratchBytes = (4u << 20) + 4096;   // partial tiles of the LLaMA decode shapes + counters
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+static int static_scratch_ptr(void** out) {
+  static std::mutex mu;
+  static std::map<int, void*> per_device;
+  int dev = 0;
+  QR_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lk(mu);
+  auto it = per_device.find(dev);
+  if (it == per_device.end()) {
+    void* ptr = nullptr;
+    QR_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    it = per_device.emplace(dev, ptr).first;
+  }
+  *out = it->second;
+  return QR_OK;
+}
+}  // namespace qr
+
+int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
+                            int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
+  const size_t need = qr_linear_workspace_bytes(M, N, K);
+  if (need > qr::kStaticScratchBytes)
+    return qr::fail(QR_EUNSUPPORTED,
+                    "qr_linear_i4_f16_static: this shape needs %zu bytes of scratch, the built-in scratch holds %zu; "
+                    "use qr_linear_i4_f16_ws with a caller-provided workspace", need, qr::kStaticScratchBytes);
+  if (need == 0)   // shape runs in a single pass, no scratch involved
+    return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_static", A, B, M, N, K, out, ldo, sA, sB, bias,
+                                      (cudaStream_t)stream);
+  void* scratch = nullptr;
+  const int rc = qr::static_scratch_ptr(&scratch);
+  if (rc != QR_OK) return rc;
+  // every call shares the array and finds the previous call's contents in it: the arrival counters at its
+  // start must be zero when the kernel begins (the partial tiles behind them are fully overwritten)
+  size_t counter_bytes = 0;
+  qr::decode_splits(M, N, K, nullptr, &counter_bytes);
+  QR_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, (cudaStream_t)stream));
+  return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_static", A, B, M, N, K, out, ldo, sA, sB, bias,
+                                    (cudaStream_t)stream, scratch, qr::kStaticScratchBytes);
 }
 
 int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
