@@ -57,6 +57,11 @@ int qr_kernel_status(int* status_out);
  * Unknown keys return QR_EINVAL. No upstream counterpart. */
 int qr_set_tuning(const char* key, int value);
 
+/* Debugging aid: when non-null, the 2-CTA GEMM writes clock64 stamps of the first 64 k-blocks of its
+ * first cluster into this device buffer (2 x 8 x 64 int64).  Pass NULL to switch it off.  No upstream
+ * counterpart. */
+int qr_debug_set_trace(void* device_buffer);
+
 /* ------------------------------------------------------------------ (a) ---
  * Online Hadamard transform over the last axis, y = x (hadK (x) H_{n/K})^T/sqrt(n).
  * Replaces fast_hadamard_transform.hadamard_transform + `hadK @` as called by

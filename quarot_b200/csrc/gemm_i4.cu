@@ -57,6 +57,7 @@ struct GemmParams {
   int splits;            // 1-CTA kernel: k splits per tile (1 = none); > 1 needs the scratch buffers below
   int32_t* ws_partial;   // [tiles][splits][BN][128] int32 partial tiles
   int* ws_counter;       // [tiles] arrival counters, zero before and after every launch
+  long long* trace;      // optional device buffer [2 CTAs][8 slots][64] for clock64 stamps of cluster 0, or null
   int debug;             // timing experiments only (results are wrong when non-zero)
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int* status;
@@ -414,8 +415,11 @@ struct SmemLayout2 {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
+constexpr int kThreads2 = kThreads + 32;          // one more warp: the second MMA issuer
+constexpr int kIssuerBWarp = kThreads / 32;       // its warp index (14)
+
 template <int PST, int IST, int MODE>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads2, 1)
 gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
   using L = SmemLayout2<PST, IST>;
   constexpr int ACC = 2;
@@ -437,13 +441,15 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   auto acc_empty = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + 2 + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
+  volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps / 2); }
     for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), kWidenWarps); mbar_init(empty_i(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 2 * kEpiWarps); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 2); mbar_init(acc_empty(a), 2 * kEpiWarps); }
     *abort_flag = 0;
+    *turn = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -456,6 +462,11 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // optional timeline (debugging aid): cluster 0 records clock64 stamps of its first 64 k-blocks
+  long long* trace = (p.trace && (blockIdx.x >> 1) == 0) ? p.trace + (size_t)(blockIdx.x & 1) * 8 * 64 : nullptr;
+  auto stamp = [&](int lane_id, uint32_t it_, int slot) {
+    if (trace && lane_id == 0 && it_ < 64) trace[(size_t)slot * 64 + it_] = clock64();
+  };
   const int num_tiles = p.tilesP * p.tilesQ;     // pair tiles
   const int num_kb = (p.K + 127) >> 7;
   const int cluster_id = blockIdx.x >> 1;
@@ -472,6 +483,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           const int s = it % PST;
           const uint32_t ph = (it / PST) & 1;
           if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
+          stamp(0, it, 0);
           mbar_expect_tx(full_p(s), L::kPkStage);
           const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
           tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * 2 * kBM + (int)rank * kBM);
@@ -479,9 +491,16 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA only)
+  } else if (warp == 1 || warp == kIssuerBWarp) {
+    // ------------------------------------------------------------ MMA issuers (leader CTA only)
+    // Issuing is the critical path of the main loop: per k-block one thread spends several hundred cycles in
+    // the barrier wait, the four tcgen05.mma and the commit, more than the MMAs take to execute.  Two threads of
+    // different warps therefore take alternate k-blocks.  A shared turn counter keeps the MMAs in k order:
+    // a thread issues block `it` only when turn == it, brackets the hand-over with tcgen05.fence
+    // before/after_thread_sync (which orders the asynchronous MMAs of the two threads), and does its wait for
+    // the next block and its commit while the other thread issues.
     if (leader && lane == 0) {
+      const int me = (warp == 1) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc_i8(2 * kBM, kBN2);
       const uint32_t peer_empty_i0 = mapa_cluster(empty_i(0), 1);
       const uint32_t peer_acc_full0 = mapa_cluster(acc_full(0), 1);
@@ -490,36 +509,61 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
         const int a = tl % ACC;
         const uint32_t pha = (tl / ACC) & 1;
-        if (!((p.sync_mode & 2) ? mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 12)
-                                 : mbar_wait_cluster(acc_empty(a), pha ^ 1, abort_flag, p.status, 12))) { ok = false; break; }
-        tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * kBN2;
+        bool mine_in_tile = false;
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          if ((int)(it & 1u) != me) continue;
+          mine_in_tile = true;
           const int s = it % IST;
           const uint32_t ph = (it / IST) & 1;
-          if (!((p.sync_mode & 2) ? mbar_wait(full_i(s), ph, abort_flag, p.status, 13)
-                                   : mbar_wait_cluster(full_i(s), ph, abort_flag, p.status, 13))) { ok = false; break; }
+          if (kb < 2) {   // first block of this thread in the tile: the accumulator buffer must have been drained
+            if (!mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
+          }
+          if (!mbar_wait(full_i(s), ph, abort_flag, p.status, 13)) { ok = false; break; }
+          // my turn?
+          {
+            const long long t0 = clock64();
+            bool got = (*turn == it);
+            for (uint32_t spin = 1; !got; ++spin) {
+              got = (*turn == it);
+              if (!got && (spin & 255u) == 0u) {
+                if (*abort_flag) break;
+                if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(p.status, 17); break; }
+              }
+            }
+            if (!got) { ok = false; break; }
+          }
           tc_fence_after();
+          stamp(0, it, 1);
           const uint32_t a_addr = smem_base + L::kI8Off + s * L::kI8Stage;
           const uint64_t da = make_kmajor_sw128_desc(a_addr);
           const uint64_t db = make_kmajor_sw128_desc(a_addr + kBM * 128);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4)
             umma_i8_2sm(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+          tc_fence_before();
+          *turn = it + 1;
+          stamp(0, it, 2);
           if (p.sync_mode & 4) {
             umma_commit_2sm_mc(empty_i(s), 3);
           } else {
             umma_commit_2sm(empty_i(s));
             umma_commit_2sm(peer_empty_i0 + 8u * s);
           }
+          stamp(0, it, 3);
         }
-        if (ok) {
+        if (!ok) break;
+        // accumulator ready: acc_full needs both issuers (a commit only tracks the MMAs of its own thread)
+        if (mine_in_tile) {
           if (p.sync_mode & 4) {
             umma_commit_2sm_mc(acc_full(a), 3);
           } else {
             umma_commit_2sm(acc_full(a));
             umma_commit_2sm(peer_acc_full0 + 8u * a);
           }
+        } else {
+          mbar_arrive(acc_full(a));
+          mbar_arrive_cluster_relaxed(peer_acc_full0 + 8u * a);
         }
       }
     }
@@ -605,7 +649,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
       }
     }
-  } else {
+  } else if (warp < 2 + kEpiWarps + kWidenWarps) {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
     // Two groups of four warps take alternate k-blocks, so that a group has two MMA periods per
     // stage.  Packed data is read into registers before the int8 slot is waited for, which keeps
@@ -626,12 +670,14 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
+        if (gt == 0) stamp(0, it, 4);
         const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
         uint4 w[kPer];
 #pragma unroll
         for (int j = 0; j < kPer; ++j) w[j] = *reinterpret_cast<const uint4*>(pk + (gt + j * kGThreads) * 16);
         if (!mbar_wait(empty_i(si), phi ^ 1, abort_flag, p.status, 16)) { ok = false; break; }
         tc_fence_after();
+        if (gt == 0) stamp(0, it, 5);
         unsigned char* i8 = smem_gen + L::kI8Off + si * L::kI8Stage;
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
@@ -656,6 +702,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           // so the loads have certainly completed
           mbar_arrive(empty_p(sp_));
         }
+        if (gt == 0) stamp(0, it, 6);
       }
     }
   }
@@ -1154,7 +1201,7 @@ static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const
   using L = SmemLayout2<PST, IST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
   static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads, L::kDynamic, max_clusters, tmP, tmQ, p, grid_cap, st);
+  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, tmP, tmQ, p, grid_cap, st);
 }
 
 template <typename Kern>
@@ -1204,6 +1251,8 @@ static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t*
   return splits;
 }
 
+static void* g_trace_ptr = nullptr;   // set through qr_debug_set_trace (debugging aid)
+
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
@@ -1227,6 +1276,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   p.splits = 1; p.ws_partial = nullptr; p.ws_counter = nullptr;
   p.sync_mode = tuning("gemm_sync", 7);
   p.debug = tuning("gemm_debug", 0);
+  p.trace = reinterpret_cast<long long*>(g_trace_ptr);
   p.bias = reinterpret_cast<const __half*>(bias);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
@@ -1301,6 +1351,11 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
                      int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16", A, B, M, N, K, out, ldo, sA, sB, bias,
                                     (cudaStream_t)stream);
+}
+
+int qr_debug_set_trace(void* device_buffer) {
+  qr::g_trace_ptr = device_buffer;
+  return QR_OK;
 }
 
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
