@@ -415,8 +415,10 @@ struct SmemLayout2 {
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-constexpr int kThreads2 = kThreads + 32;          // one more warp: the second MMA issuer
-constexpr int kIssuerBWarp = kThreads / 32;       // its warp index (14)
+constexpr int kWidenGroups2 = 3;                                  // widen groups of four warps, taking k-blocks round-robin
+constexpr int kWidenWarps2 = 4 * kWidenGroups2;
+constexpr int kIssuerBWarp = 2 + kEpiWarps + kWidenWarps2;        // warp index of the second MMA issuer
+constexpr int kThreads2 = 32 * (kIssuerBWarp + 1);
 
 template <int PST, int IST, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
@@ -445,8 +447,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps / 2); }
-    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), kWidenWarps); mbar_init(empty_i(s), 1); }
+    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 4); }   // four warps of the owning group
+    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), 8); mbar_init(empty_i(s), 1); }      // 4 local + 4 remote warps
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 2); mbar_init(acc_empty(a), 2 * kEpiWarps); }
     *abort_flag = 0;
     *turn = 0;
@@ -649,24 +651,23 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
       }
     }
-  } else if (warp < 2 + kEpiWarps + kWidenWarps) {
+  } else if (warp < 2 + kEpiWarps + kWidenWarps2) {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
-    // Two groups of four warps take alternate k-blocks, so that a group has two MMA periods per
-    // stage.  Packed data is read into registers before the int8 slot is waited for, which keeps
-    // the shared-memory read off the slot-reuse critical path.
+    // Groups of four warps take the k-blocks round-robin, so that a group has kWidenGroups2 MMA periods
+    // per stage (its stores and the proxy fence take more than one).  Packed data is read into registers
+    // before the int8 slot is waited for, which keeps the shared-memory read off the slot-reuse path.
     const int wt = threadIdx.x - 32 * (2 + kEpiWarps);
-    const int group = (wt >> 5) & 1;
-    const int gt = (wt & 31) | ((wt >> 6) << 5);        // 0 .. 127 inside the group
+    const int group = wt >> 7;                          // four warps per group
+    const int gt = wt & 127;                            // 0 .. 127 inside the group
     constexpr int kChunks = kRows2 * 4;                 // 1024 packed 16-byte chunks per stage
-    constexpr int kGThreads = 32 * kWidenWarps / 2;     // 128
+    constexpr int kGThreads = 128;
     constexpr int kPer = kChunks / kGThreads;           // 8 chunks per thread
-    static_assert(PST % 2 == 0 && IST % 2 == 0, "alternating groups need even ring sizes");
     const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
     uint32_t it = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        if ((int)(it & 1u) != group) continue;
+        if ((int)(it % kWidenGroups2) != group) continue;
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
