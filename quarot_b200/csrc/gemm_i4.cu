@@ -676,6 +676,22 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         uint4 w[kPer];
 #pragma unroll
         for (int j = 0; j < kPer; ++j) w[j] = *reinterpret_cast<const uint4*>(pk + (gt + j * kGThreads) * 16);
+        // Hand the staging slot back to the TMA producer as soon as the packed data is in registers.  The
+        // arrive must not overtake the loads, so it is made to depend on every loaded word: the words are
+        // folded into one value that feeds a (practically never taken) predicated store.
+        {
+          uint32_t fold = 0;
+#pragma unroll
+          for (int j = 0; j < kPer; ++j) fold ^= w[j].x ^ w[j].y ^ w[j].z ^ w[j].w;
+          asm volatile(
+              "{\n\t.reg .pred p;\n\t"
+              "setp.eq.u32 p, %0, 0xC0FFEE11;\n\t"
+              "@p st.volatile.shared.u32 [%1], %0;\n\t}"
+              ::"r"(fold), "r"(smem_base + L::kAbortOff + 8)
+              : "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(empty_p(sp_));
+        }
         if (!mbar_wait(empty_i(si), phi ^ 1, abort_flag, p.status, 16)) { ok = false; break; }
         tc_fence_after();
         if (gt == 0) stamp(0, it, 5);
@@ -699,9 +715,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         if (lane == 0) {
           if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * si);
           else mbar_arrive_cluster(leader_full_i0 + 8u * si);
-          // the staging slot is released only here: the stores above consumed every loaded register,
-          // so the loads have certainly completed
-          mbar_arrive(empty_p(sp_));
         }
         if (gt == 0) stamp(0, it, 6);
       }
