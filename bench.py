@@ -39,6 +39,9 @@ WORKLOADS = {
     "config0": ("CONFIG0", 2048),
     "llama2_7b_decode": ("LLAMA2_7B", 32),
     "llama2_70b_prefill": ("LLAMA2_70B", 4096),
+    # BASELINE config 4: the two 70B MLP linears with their output channels split over the ranks and an
+    # all-gather of the fp16 result; every rank sees all token rows (use --tokens to sweep M)
+    "llama2_70b_mlp_colsplit": ("LLAMA2_70B_MLP", 4096),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -260,6 +263,59 @@ def e2e_run(qb, layers, M, dev, steps, warmup, work):
     return e0.elapsed_time(e1) / steps, h2d_bytes, d2h_bytes
 
 
+def colsplit_run(args, layers, M, dev, world, rank, dist):
+    """Column split: rank r owns N/G output channels of each linear; kernel (a) runs on all M rows on every
+    rank, the local GEMM produces [M, N/G], the slabs are all-gathered and interleaved into [M, N].
+    Times the local compute alone and compute + collective (CUDA events, max over ranks)."""
+    import quarot_b200 as qb
+    from quarot_b200 import dist as qd, synth
+    from quarot_b200.functional import hadamard as FH
+    mods = []
+    for li, (name, K, N, had) in enumerate(layers):
+        khad = FH.get_hadK(K)[1] if had else 0
+        table = FH.device_table(khad, dev) if khad > 1 else None
+        x = synth.activations_device(M, K, seed=1234 + li, device=dev)
+        w, sw = synth.weights_device(N // world, K, seed=4321 + li + 100 * rank, device=dev)
+        lin = qd.ColumnSplitLinear4bit.__new__(qd.ColumnSplitLinear4bit)
+        torch.nn.Module.__init__(lin)
+        lin.group, lin.world, lin.rank = None, world, rank
+        lin.register_buffer("weight", w)
+        lin.register_buffer("weight_scales", sw)
+        lin.bias, lin.out_features, lin._compute = None, N, qb.linear_i4
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+        mods.append((name, K, N, khad, table, x, lin, out))
+
+    def step(collective):
+        for (name, K, N, khad, table, x, lin, out) in mods:
+            q, s, _ = qb.hadamard_quant(x, table, khad, 1.0)
+            pq = qb.PackedQuantizedTensor(q, s)
+            if collective:
+                lin(pq, gathered_out=out)
+            else:
+                lin.local_forward(pq)
+
+    res = {}
+    for label, coll in (("compute_ms", False), ("compute_plus_allgather_ms", True)):
+        for _ in range(max(args.warmup, 3)):
+            step(coll)
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step(coll)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / args.steps
+        if dist is not None:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        res[label] = ms
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -318,6 +374,26 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "llama2_70b_mlp_colsplit":
+        res = colsplit_run(args, layers, M, dev, world, rank, dist)
+        ops = layer_ops(layers, M)           # whole job: every output channel is computed exactly once
+        ms = res["compute_plus_allgather_ms"]
+        line = {"metric": metric, "value": ops / (ms * 1e-3) / 1e12, "unit": "TOPS", "n_gpus": n_gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None,
+                "dtype": "int4 codes widened to int8, int32 accumulate, fp16 out", "data": "synthetic",
+                "config": dict(config, sharding="output channels split over ranks, NCCL all-gather of the fp16 slabs, "
+                                                "every rank quantises all token rows"),
+                "compute_only": {"ms_per_step": res["compute_ms"], "value": ops / (res["compute_ms"] * 1e-3) / 1e12,
+                                 "unit": "TOPS"},
+                "allgather_bytes_per_rank": sum(2 * M * N // n_gpus for (_, _, N, _) in layers),
+                "tokens_per_s": M / (ms * 1e-3), "gpu_launches": 2 * len(layers) * args.steps}
+        if rank == 0:
+            print(json.dumps(line))
+        if dist is not None:
+            dist.destroy_process_group()
+        return 0
 
     nsets = 3
     work = build_device_workload(layers, M, dev, nsets)

@@ -60,6 +60,7 @@ struct GemmParams {
   long long* trace;      // optional device buffer [2 CTAs][8 slots][64] for clock64 stamps of cluster 0, or null
   int debug;             // timing experiments only (results are wrong when non-zero)
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
+  int tma_out;           // 2-CTA kernel: the output has a tensor map (16-byte aligned base and row pitch): tiled stores
   int* status;
 };
 
@@ -407,7 +408,10 @@ struct SmemLayout2 {
   static constexpr int kPkStage = kRows2 * kBKBytes;
   static constexpr int kI8Off = 0;
   static constexpr int kPkOff = IST * kI8Stage;
-  static constexpr int kBarOff = kPkOff + PST * kPkStage;
+  static constexpr int kStageOff = kPkOff + PST * kPkStage;          // per epilogue warp: 32 rows x 128 B of output, 128B-swizzled
+  static constexpr int kScaleOff = kStageOff + kEpiWarps * 4096;     // per epilogue warp: the tile's 256 column scales as fp32
+  static constexpr int kBiasOff = kScaleOff + kEpiWarps * 1024;      // per epilogue warp: the tile's 256 bias values (fp16)
+  static constexpr int kBarOff = kBiasOff + kEpiWarps * 512;
   static constexpr int kNumBars = 2 * PST + 2 * IST + 4;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
@@ -422,7 +426,8 @@ constexpr int kThreads2 = 32 * (kIssuerBWarp + 1);
 
 template <int PST, int IST, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
-gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
+gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
+                   const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
   using L = SmemLayout2<PST, IST>;
   constexpr int ACC = 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -445,6 +450,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
   volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[7 * 64 + 0] = clock64();   // life-cycle stamps live in slot 7
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 4); }   // four warps of the owning group
@@ -473,6 +479,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   const int num_kb = (p.K + 127) >> 7;
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
+  if (threadIdx.x == 0) stamp(0, 1, 7);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (own rows only)
@@ -571,72 +578,129 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     }
   } else if (warp < 2 + kEpiWarps) {
     // ------------------------------------------------------------ epilogue (own 128 accumulator rows)
+    // Warp q4 owns accumulator lanes 32 q4 .. 32 q4 + 31 (one output row per thread).  With a tensor map over
+    // the output the rows are written as tiled stores: the warp converts 128 bytes of every row (64 fp16 or
+    // 32 int32 columns), puts them into a 128B-swizzled 4 KB staging block of shared memory (conflict-free
+    // 16-byte stores) and one thread hands the block to the TMA unit, which writes whole 128-byte row segments
+    // and clips what lies outside the matrix.  The load/store pipe of the SM, which the widen warps saturate,
+    // then sees 16 store wavefronts per block instead of 128 scattered 16-byte global stores.
+    // The tile's 256 column scales (and bias) are fetched into shared memory before the accumulator is waited for.
     const int q4 = warp & 3;
     const int prow_in_tile = q4 * 32 + lane;
     const uint32_t leader_acc_empty0 = mapa_cluster(acc_empty(0), 0);
+    constexpr int CW = (MODE == MODE_I32) ? 32 : 64;     // columns per staged block (128 bytes per row)
+    unsigned char* stg = smem_gen + L::kStageOff + q4 * 4096;
+    const uint32_t stg_u32 = smem_base + L::kStageOff + q4 * 4096;
+    float* sqf = reinterpret_cast<float*>(smem_gen + L::kScaleOff + q4 * 1024);
+    __half* bsh = reinterpret_cast<__half*>(smem_gen + L::kBiasOff + q4 * 512);
+    const uint32_t my_sw = (uint32_t)(lane & 7);
     uint32_t tl = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
       const int tp = tile % p.tilesP, tq = tile / p.tilesP;
       const int a = tl % ACC;
       const uint32_t pha = (tl / ACC) & 1;
+      if (MODE == MODE_F16 && p.tma_out) {
+        __syncwarp();   // the previous tile's reads of the scale block are done
+#pragma unroll
+        for (int j = lane; j < kBN2; j += 32) {
+          const int col = tq * kBN2 + j;
+          sqf[j] = col < p.rowsQ ? __half2float(p.sQ[col]) : 0.0f;
+          if (p.bias) bsh[j] = col < p.rowsQ ? p.bias[col] : __float2half(0.0f);
+        }
+        __syncwarp();
+      }
       if (!mbar_wait(acc_full(a), pha, abort_flag, p.status, 14)) { ok = false; break; }
       tc_fence_after();
+      if (q4 == 0) stamp(lane, 8 + 2 * tl, 7);
       const int prow = tp * 2 * kBM + (int)rank * kBM + prow_in_tile;
       const bool prow_ok = prow < p.rowsP;
       float sp = 0.0f;
       if (MODE == MODE_F16 && prow_ok) sp = __half2float(p.sP[prow]);
+      auto release_acc = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_acc_empty0 + 8u * a);
+          else mbar_arrive_cluster(leader_acc_empty0 + 8u * a);
+        }
+        if (q4 == 0) stamp(lane, 9 + 2 * tl, 7);
+      };
+      if (p.tma_out) {
+        const int row0 = tp * 2 * kBM + (int)rank * kBM + q4 * 32;
 #pragma unroll 1
-      for (int c0 = 0; c0 < kBN2; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0), r);
-        tmem_ld_wait();
-        if (c0 + 32 >= kBN2) {
-          tc_fence_before();
+        for (int c0 = 0; c0 < kBN2; c0 += CW) {
+#pragma unroll
+          for (int h = 0; h < CW / 32; ++h) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0 + 32 * h), r);
+            tmem_ld_wait();
+            if (c0 + CW >= kBN2 && h == CW / 32 - 1) release_acc();
+            if (MODE == MODE_I32) {
+              if (lane == 0) bulk_wait_read_all();   // the TMA unit has read the previous block out of the staging area
+              __syncwarp();
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const uint4 v = make_uint4((uint32_t)((int32_t)r[4 * e] >> 8), (uint32_t)((int32_t)r[4 * e + 1] >> 8),
+                                           (uint32_t)((int32_t)r[4 * e + 2] >> 8), (uint32_t)((int32_t)r[4 * e + 3] >> 8));
+                *reinterpret_cast<uint4*>(stg + lane * 128 + ((((uint32_t)e) ^ my_sw) << 4)) = v;
+              }
+            } else {
+              uint4 pk[4];
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                __half2* hh = reinterpret_cast<__half2*>(&pk[e]);
+                const int jc = c0 + 32 * h + 8 * e;     // column inside the tile
+                const float4 s0 = *reinterpret_cast<const float4*>(sqf + jc);
+                const float4 s1 = *reinterpret_cast<const float4*>(sqf + jc + 4);
+                hh[0] = __floats2half2_rn((float)((int32_t)r[8 * e + 0] >> 8) * (sp * s0.x),
+                                          (float)((int32_t)r[8 * e + 1] >> 8) * (sp * s0.y));
+                hh[1] = __floats2half2_rn((float)((int32_t)r[8 * e + 2] >> 8) * (sp * s0.z),
+                                          (float)((int32_t)r[8 * e + 3] >> 8) * (sp * s0.w));
+                hh[2] = __floats2half2_rn((float)((int32_t)r[8 * e + 4] >> 8) * (sp * s1.x),
+                                          (float)((int32_t)r[8 * e + 5] >> 8) * (sp * s1.y));
+                hh[3] = __floats2half2_rn((float)((int32_t)r[8 * e + 6] >> 8) * (sp * s1.z),
+                                          (float)((int32_t)r[8 * e + 7] >> 8) * (sp * s1.w));
+                if (p.bias) {
+                  const uint4 bb = *reinterpret_cast<const uint4*>(bsh + jc);
+                  const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) hh[q] = __hadd2(hh[q], bh[q]);
+                }
+              }
+              if (h == 0) {
+                if (lane == 0) bulk_wait_read_all();
+                __syncwarp();
+              }
+#pragma unroll
+              for (int e = 0; e < 4; ++e)
+                *reinterpret_cast<uint4*>(stg + lane * 128 + ((((uint32_t)(4 * h + e)) ^ my_sw) << 4)) = pk[e];
+            }
+          }
+          fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) {
-            if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_acc_empty0 + 8u * a);
-            else mbar_arrive_cluster(leader_acc_empty0 + 8u * a);
+          if (lane == 0 && row0 < p.rowsP && tq * kBN2 + c0 < p.rowsQ) {
+            tma_store_2d(&tmO, stg_u32, tq * kBN2 + c0, row0);
+            bulk_commit_group();
           }
         }
-        const int qcol0 = tq * kBN2 + c0;
-        if (prow_ok) {
-          if (MODE == MODE_I32) {
-            int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-            if (qcol0 + 32 <= p.rowsQ && p.vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
-                                                            (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
-            } else {
+      } else {
+        // output without a tensor map (unaligned base or row pitch): element-wise stores
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN2; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0), r);
+          tmem_ld_wait();
+          if (c0 + 32 >= kBN2) release_acc();
+          const int qcol0 = tq * kBN2 + c0;
+          if (prow_ok) {
+            if (MODE == MODE_I32) {
+              int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
 #pragma unroll
               for (int j = 0; j < 32; ++j)
                 if (qcol0 + j < p.rowsQ) o[j] = (int32_t)r[j] >> 8;
-            }
-          } else {
-            __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-            if ((qcol0 + 32 <= p.rowsQ) && p.vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __half2* h = reinterpret_cast<__half2*>(&pk);
-                const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + j));
-                const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 sc = __half22float2(sqh[e]);
-                  h[e] = __floats2half2_rn((float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x),
-                                           (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y));
-                }
-                if (p.bias) {
-                  const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + j));
-                  const __half2* bh = reinterpret_cast<const __half2*>(&bb);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
-                }
-                *reinterpret_cast<uint4*>(o + j) = pk;
-              }
             } else {
+              __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 if (qcol0 + j < p.rowsQ) {
@@ -650,7 +714,9 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           }
         }
       }
+      if (q4 == 0) stamp(lane, 32 + tl, 7);
     }
+    if (lane == 0) bulk_wait_all();   // the tiled stores of this thread are complete before the CTA exits
   } else if (warp < 2 + kEpiWarps + kWidenWarps2) {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
     // Groups of four warps take the k-blocks round-robin, so that a group has kWidenGroups2 MMA periods
@@ -726,6 +792,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   __syncthreads();
   __syncwarp();
   cluster_sync_all();   // the peer may still read this CTA's shared memory or arrive on its barriers
+  if (threadIdx.x == 0) stamp(0, 63, 7);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -1178,6 +1245,23 @@ static int make_packed_map(CUtensorMap* map, const void* base, int64_t rows, int
   return QR_OK;
 }
 
+// Tensor map over the output matrix [rows, cols] with a row pitch of ldo elements (fp16 or int32), box = 128 bytes
+// of a row x 32 rows, 128-byte swizzle: what one epilogue warp of the 2-CTA kernel stores at a time.
+static int make_out_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldo, bool is_i32) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(QR_ENOTREADY, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t esz = is_i32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ldo * esz};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, is_i32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(QR_EINVAL, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+  return QR_OK;
+}
+
 template <int BN, int PST, int IST, int ACC, bool SWAP, int MODE>
 static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
   using L = SmemLayout<BN, PST, IST>;
@@ -1198,29 +1282,31 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
   return QR_OK;
 }
 
-template <typename Kern>
-static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const CUtensorMap& tmP,
-                           const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st);
+template <typename Kern, typename... Maps>
+static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const GemmParams& p, int grid_cap,
+                           cudaStream_t st, const Maps&... maps);
 
 template <int PST, int MODE>
 static int launch_gemm_2sm_ts(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
   using L = SmemLayoutTS<PST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
   static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_ts_kernel<PST, MODE>, kThreadsTS, L::kDynamic, max_clusters, tmP, tmQ, p, grid_cap, st);
+  return launch_cluster2(gemm_i4_2sm_ts_kernel<PST, MODE>, kThreadsTS, L::kDynamic, max_clusters, p, grid_cap, st, tmP, tmQ);
 }
 
 template <int PST, int IST, int MODE>
-static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
+static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmO, const GemmParams& p,
+                           int grid_cap, cudaStream_t st) {
   using L = SmemLayout2<PST, IST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
+  static_assert(L::kStageOff % 1024 == 0, "staging blocks must be 1024-byte aligned for the 128-byte swizzle");
   static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, tmP, tmQ, p, grid_cap, st);
+  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, p, grid_cap, st, tmP, tmQ, tmO);
 }
 
-template <typename Kern>
-static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const CUtensorMap& tmP,
-                           const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
+template <typename Kern, typename... Maps>
+static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const GemmParams& p, int grid_cap,
+                           cudaStream_t st, const Maps&... maps) {
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
   cudaLaunchConfig_t cfg = {};
@@ -1246,7 +1332,7 @@ static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clus
   if (clusters > nclusters) clusters = nclusters;
   if (grid_cap > 0 && clusters > grid_cap) clusters = grid_cap;
   cfg.gridDim = dim3(2 * clusters);
-  QR_CUDA(cudaLaunchKernelEx(&cfg, kern, tmP, tmQ, p));
+  QR_CUDA(cudaLaunchKernelEx(&cfg, kern, maps..., p));
   return QR_OK;
 }
 
@@ -1292,6 +1378,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   p.debug = tuning("gemm_debug", 0);
   p.trace = reinterpret_cast<long long*>(g_trace_ptr);
   p.bias = reinterpret_cast<const __half*>(bias);
+  p.tma_out = 0;
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
   CUtensorMap tmP, tmQ;
@@ -1308,8 +1395,15 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
     if (ts) {
       return launch_gemm_2sm_ts<2, MODE>(tmP, tmQ, p, grid_cap, st);
     }
-    if (tuning("gemm_pst", 4) == 6) return launch_gemm_2sm<6, 4, MODE>(tmP, tmQ, p, grid_cap, st);
-    return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, p, grid_cap, st);
+    // tiled stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element-wise
+    CUtensorMap tmO;
+    p.tma_out = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) && tuning("gemm_tma_out", 1) != 0;
+    if (p.tma_out) {
+      if ((rc = make_out_map(&tmO, out, M, N, ldo, MODE == MODE_I32))) return rc;
+    } else {
+      tmO = tmP;   // never dereferenced
+    }
+    return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, tmO, p, grid_cap, st);
   }
   if (!swap) {
     int bn = tuning("gemm_bn", 256);

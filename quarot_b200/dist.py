@@ -89,6 +89,11 @@ class ColumnSplitLinear4bit(torch.nn.Module):
         lead = local.shape[:-1]
         local2 = local.reshape(-1, local.shape[-1]).contiguous()
         m, n_loc = local2.shape
+        if self.world == 1:
+            if gathered_out is None:
+                return local
+            gathered_out.view(m, n_loc).copy_(local2)
+            return gathered_out.view(*lead, self.out_features)
         slabs = torch.empty((self.world, m, n_loc), dtype=local2.dtype, device=local2.device)
         dist.all_gather_into_tensor(slabs.view(self.world * m, n_loc), local2, group=self.group)
         out = gathered_out if gathered_out is not None else torch.empty((m, self.out_features), dtype=local2.dtype,

@@ -67,14 +67,14 @@ TILE_CONFIGS = {
     "2sm_ts": {"gemm_ts": 1},
     "2sm_ts_grid3": {"gemm_ts": 1, "gemm_grid": 3},
     "2sm_ss_grid3": {"gemm_grid": 3},
-    "2sm_ss_pst6": {"gemm_pst": 6},
+    "2sm_ss_elementwise_stores": {"gemm_tma_out": 0},
     "1sm_bn256": {"gemm_2sm": 0},
     "1sm_bn128": {"gemm_2sm": 0, "gemm_bn": 128},
     "1sm_bn64": {"gemm_2sm": 0, "gemm_bn": 64},
     "1sm_pst3": {"gemm_2sm": 0, "gemm_pst": 3},
     "1sm_grid3": {"gemm_2sm": 0, "gemm_grid": 3},
 }
-TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_ts": 0, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0}
+TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_ts": 0, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0, "gemm_tma_out": 1}
 
 
 @pytest.mark.parametrize("tiles", sorted(TILE_CONFIGS))
@@ -93,6 +93,25 @@ def test_matmul_other_tile_configs_agree(tiles):
             _lib.set_tuning(k, v)
     assert torch.equal(c, want)
     assert torch.equal(o, O.sym_dequant_fp32(want, sx, sw).half())
+    assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,pitch", [(300, 1000, 512, 2048), (520, 264, 256, 272), (257, 72, 128, 84)])
+def test_linear_into_a_strided_output(M, N, K, pitch):
+    """The result may land in a column block of a wider matrix (row pitch > N): everything outside the
+    block stays untouched, for the tiled-store epilogue (pitch a multiple of 8) and the element-wise one."""
+    a, w = _rand_packed(M, K, 5), _rand_packed(N, K, 6)
+    sx = (torch.rand(M) * 0.5 + 0.05).half()
+    sw = (torch.rand(N) * 0.015 + 0.005).half()
+    bias = torch.randn(N).half()
+    want = O.sym_dequant_fp32(O.matmul_i4(a, w), sx, sw).half() + bias
+    off = 8
+    buf = torch.full((M, pitch), 7.0, dtype=torch.float16, device=DEV)
+    view = buf[:, off:off + N]
+    qb.linear_i4(a.to(DEV), sx.to(DEV), w.to(DEV), sw.to(DEV), bias.to(DEV), out=view)
+    got = buf.cpu()
+    assert torch.equal(got[:, off:off + N], want)
+    assert bool((got[:, :off] == 7.0).all()) and bool((got[:, off + N:] == 7.0).all())
     assert _lib.kernel_status() == 0
 
 
