@@ -62,6 +62,13 @@ int qr_set_tuning(const char* key, int value);
  * counterpart. */
 int qr_debug_set_trace(void* device_buffer);
 
+/* Self-test: the quantisers divide by the row scale with one multiplication by the rounded reciprocal.  This
+ * runs every finite fp16 value against every finite non-zero fp16 scale on the current device and counts the
+ * pairs whose int4 code differs from the one IEEE division gives (expected: 0).  Synchronises the device;
+ * uses the legacy default stream.  No upstream counterpart (upstream divides with the `/` operator,
+ * quarot/kernels/quant.cu:38-39). */
+int qr_debug_division_check(uint64_t* mismatches_out);
+
 /* ------------------------------------------------------------------ (a) ---
  * Online Hadamard transform over the last axis, y = x (hadK (x) H_{n/K})^T/sqrt(n).
  * Replaces fast_hadamard_transform.hadamard_transform + `hadK @` as called by

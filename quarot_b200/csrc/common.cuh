@@ -30,6 +30,34 @@ int tuning(const char* key, int dflt);
     if (_e != cudaSuccess) return ::qr::cuda_fail(_e, name);     \
   } while (0)
 
+// Programmatic dependent launch.  Every kernel of the quantise -> GEMM chain is launched with the
+// "programmatic stream serialization" attribute, tells the scheduler at its very start that the next kernel
+// of the stream may be brought up (pdl_launch_dependents), and executes pdl_wait before its first access to
+// global memory that an earlier kernel may have written or may still read.  The wait returns when the
+// preceding kernel has completed and its memory is visible, so launch latency, barrier and tensor-memory
+// set-up of a kernel overlap the tail of its predecessor.  Without the launch attribute both are no-ops.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// cudaLaunchKernelEx with the programmatic-serialization attribute when `pdl` is set.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                        bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 static inline bool is_pow2(int64_t v) { return v > 0 && (v & (v - 1)) == 0; }
 static inline int ilog2(int64_t v) { int l = 0; while ((int64_t(1) << l) < v) ++l; return l; }
@@ -63,18 +91,67 @@ __device__ __forceinline__ uint32_t quant_pair_zero_scale(float a, float b) {
   return ca | (cb << 16);
 }
 
-// Correctly rounded fp32 quotient y / s given rcp = RN(1/s): the product y*rcp is
-// refined by two residual (Markstein) steps, which yields the IEEE round-to-nearest
-// quotient for the normal-range operands that occur here (s is a finite non-zero
-// fp16 value widened to fp32, |y| <= 65504).  Costs 5 FMA-pipe instructions and no
-// MUFU call per element, because the reciprocal is shared by the whole row.
-__device__ __forceinline__ float div_by_scale(float y, float s, float rcp) {
-  float t = y * rcp;
-  float e = __fmaf_rn(-s, t, y);
-  t = __fmaf_rn(e, rcp, t);
-  e = __fmaf_rn(-s, t, y);
-  return __fmaf_rn(e, rcp, t);
+// Division by the row scale as ONE multiplication with rcp = RN(1/s).
+// torch computes fp16(fp32(y / s)) for fp16 y and s; t = RN(y * rcp) is not always the correctly rounded
+// fp32 quotient, but it always rounds to the same fp16 value, which is all that is used:
+//   * |t - y/s| <= (2^-23 + 2^-47) |y/s|  (two roundings of 2^-24 each);
+//   * a tie point between neighbouring fp16 values is m = M 2^e with M an odd 12-bit integer; for y = Y 2^a,
+//     s = S 2^b (Y, S < 2^11) the quotient can only be near m when y - s m is a non-zero multiple of the unit
+//     of s m, so |y/s - m| >= m / (S M) > 2^-23 (1 + 2^-11) m -- further away than t can be from y/s;
+//     y/s never equals a tie point (S M would need more than 11 bits in y).
+// Hence fp16(t) == fp16(y / s) whenever the result is a normal fp16 number; below that every candidate
+// rounds to the integer 0 anyway.  The library's self-test (qr_debug_division_check) compares the resulting
+// int4 codes with those from IEEE division for every pair of finite fp16 operands.
+__device__ __forceinline__ float div_by_scale(float y, float /*s*/, float rcp) { return y * rcp; }
+
+// Two fp16 values (one 32-bit word) -> the word 0x66cc66cc whose bytes 0 and 2 hold the two int4 codes as int8.
+// CLAMP = false may be used when |y / s| < 7.5 is known (clip ratio 1 and a scale in the normal fp16 range).
+template <bool CLAMP>
+__device__ __forceinline__ uint32_t quant2_word(uint32_t hw, float rcp) {
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw));
+  __half2 h = __floats2half2_rn(f.x * rcp, f.y * rcp);
+  if (CLAMP) {
+    h = __hmax2(h, __float2half2_rn(-8.0f));
+    h = __hmin2(h, __float2half2_rn(7.0f));
+  }
+  h = __hadd2(h, __float2half2_rn(1536.0f));
+  return *reinterpret_cast<uint32_t*>(&h);
 }
+
+// Four such words (elements 0..7) -> 4 packed bytes: byte j = code(2j) | code(2j+1) << 4.
+__device__ __forceinline__ uint32_t pack8_codes(uint32_t u0, uint32_t u1, uint32_t u2, uint32_t u3) {
+  const uint32_t p01 = __byte_perm(u0, u1, 0x6240);   // [e0, e2, e1, e3]
+  const uint32_t p23 = __byte_perm(u2, u3, 0x6240);   // [e4, e6, e5, e7]
+  const uint32_t ev = __byte_perm(p01, p23, 0x5410);  // [e0, e2, e4, e6]
+  const uint32_t od = __byte_perm(p01, p23, 0x7632);  // [e1, e3, e5, e7]
+  return (ev & 0x0F0F0F0Fu) | ((od << 4) & 0xF0F0F0F0u);
+}
+
+// Eight fp16 values (four words) -> four packed bytes with torch's arithmetic.  s is the row scale
+// (s == 0 follows torch's x / 0), rcp = RN(1/s); `noclamp` as for quant2_word (must be uniform per row).
+__device__ __forceinline__ uint32_t quant8_words(uint32_t h0, uint32_t h1, uint32_t h2, uint32_t h3, float s, float rcp,
+                                                 bool noclamp) {
+  if (s == 0.0f) {
+    uint32_t out = 0;
+    const uint32_t hw[4] = {h0, h1, h2, h3};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hw[e]));
+      const uint32_t cd = quant_pair_zero_scale(f.x, f.y);
+      out |= ((cd | (cd >> 12)) & 0xFFu) << (8 * e);
+    }
+    return out;
+  }
+  if (noclamp)
+    return pack8_codes(quant2_word<false>(h0, rcp), quant2_word<false>(h1, rcp), quant2_word<false>(h2, rcp),
+                       quant2_word<false>(h3, rcp));
+  return pack8_codes(quant2_word<true>(h0, rcp), quant2_word<true>(h1, rcp), quant2_word<true>(h2, rcp),
+                     quant2_word<true>(h3, rcp));
+}
+
+// The clamp of the codes can be skipped when the clip ratio is 1 and the scale is a normal fp16 number:
+// then s >= (absmax / 7)(1 - 2^-11), so |y / s| <= 7.004 and rint gives at most 7 in magnitude.
+__device__ __forceinline__ bool clamp_free(float s, float clip) { return clip == 1.0f && s >= 6.103515625e-05f; }
 
 #endif  // __CUDACC__
 

@@ -88,6 +88,7 @@ template <int BN, int PST, int IST, int ACC, bool SWAP, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
   using L = SmemLayout<BN, PST, IST>;
+  pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -136,6 +137,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      pdl_wait();   // operands may come from the preceding kernel
       uint32_t it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
@@ -187,6 +189,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     // ------------------------------------------------------------ epilogue
     const int q4 = warp & 3;                 // TMEM lane quarter this warp may access
     const int prow_in_tile = q4 * 32 + lane; // accumulator row owned by this thread
+    pdl_wait();   // scales, output and scratch are touched only after the preceding kernel has finished
     uint32_t tl = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tl) {
@@ -450,7 +453,13 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
   volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
+  pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
   if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[7 * 64 + 0] = clock64();   // life-cycle stamps live in slot 7
+  if (threadIdx.x == 32) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO) : "memory");
+  }
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 4); }   // four warps of the owning group
@@ -484,6 +493,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (own rows only)
     if (lane == 0) {
+      pdl_wait();   // operands may come from the preceding kernel
       uint32_t it = 0;
       bool ok = true;
       for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
@@ -594,6 +604,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     float* sqf = reinterpret_cast<float*>(smem_gen + L::kScaleOff + q4 * 1024);
     __half* bsh = reinterpret_cast<__half*>(smem_gen + L::kBiasOff + q4 * 512);
     const uint32_t my_sw = (uint32_t)(lane & 7);
+    pdl_wait();   // scales and output are touched only after the preceding kernel has finished
     uint32_t tl = 0;
     bool ok = true;
     for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
@@ -716,7 +727,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
       }
       if (q4 == 0) stamp(lane, 32 + tl, 7);
     }
-    if (lane == 0) bulk_wait_all();   // the tiled stores of this thread are complete before the CTA exits
+    if (lane == 0) bulk_wait_read_all();   // the staging block must outlive the TMA unit's reads of it
   } else if (warp < 2 + kEpiWarps + kWidenWarps2) {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
     // Groups of four warps take the k-blocks round-robin, so that a group has kWidenGroups2 MMA periods
@@ -1277,21 +1288,20 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
   int grid = p.tilesP * p.tilesQ * p.splits;
   int cap = grid_cap > 0 ? grid_cap : num_sms();
   if (grid > cap) grid = cap;
-  kern<<<grid, kThreads, L::kDynamic, st>>>(tmP, tmQ, p);
-  QR_LAUNCH_CHECK("gemm_i4_kernel");
+  QR_CUDA(launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)L::kDynamic, st, tuning("pdl", 0) != 0, tmP, tmQ, p));
   return QR_OK;
 }
 
 template <typename Kern, typename... Maps>
 static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const GemmParams& p, int grid_cap,
-                           cudaStream_t st, const Maps&... maps);
+                           cudaStream_t st, bool pdl, const Maps&... maps);
 
 template <int PST, int MODE>
 static int launch_gemm_2sm_ts(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
   using L = SmemLayoutTS<PST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
   static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_ts_kernel<PST, MODE>, kThreadsTS, L::kDynamic, max_clusters, p, grid_cap, st, tmP, tmQ);
+  return launch_cluster2(gemm_i4_2sm_ts_kernel<PST, MODE>, kThreadsTS, L::kDynamic, max_clusters, p, grid_cap, st, false, tmP, tmQ);
 }
 
 template <int PST, int IST, int MODE>
@@ -1301,20 +1311,23 @@ static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
   static_assert(L::kStageOff % 1024 == 0, "staging blocks must be 1024-byte aligned for the 128-byte swizzle");
   static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, p, grid_cap, st, tmP, tmQ, tmO);
+  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, p, grid_cap, st,
+                         tuning("pdl", 0) != 0, tmP, tmQ, tmO);
 }
 
 template <typename Kern, typename... Maps>
 static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const GemmParams& p, int grid_cap,
-                           cudaStream_t st, const Maps&... maps) {
+                           cudaStream_t st, bool pdl, const Maps&... maps) {
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.blockDim = dim3(threads);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = st;
@@ -1332,6 +1345,7 @@ static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clus
   if (clusters > nclusters) clusters = nclusters;
   if (grid_cap > 0 && clusters > grid_cap) clusters = grid_cap;
   cfg.gridDim = dim3(2 * clusters);
+  cfg.numAttrs = pdl ? 2 : 1;
   QR_CUDA(cudaLaunchKernelEx(&cfg, kern, maps..., p));
   return QR_OK;
 }

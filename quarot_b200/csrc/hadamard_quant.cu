@@ -132,34 +132,15 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t add
 }
 
 // 32 fp16 values (16 half2) -> 16 packed bytes, with torch's division arithmetic.
-__device__ __forceinline__ uint4 quant32(const __half2 (&h)[16], float s, float rcp) {
-  uint32_t w[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    uint32_t packed = 0;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float2 f = __half22float2(h[4 * i + e]);
-      const uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
-                                      : quant_pair_zero_scale(f.x, f.y);
-      packed |= ((cd | (cd >> 12)) & 0xFFu) << (8 * e);
-    }
-    w[i] = packed;
-  }
-  return make_uint4(w[0], w[1], w[2], w[3]);
+__device__ __forceinline__ uint4 quant32(const __half2 (&h)[16], float s, float rcp, bool noclamp) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(h);
+  return make_uint4(quant8_words(w[0], w[1], w[2], w[3], s, rcp, noclamp), quant8_words(w[4], w[5], w[6], w[7], s, rcp, noclamp),
+                    quant8_words(w[8], w[9], w[10], w[11], s, rcp, noclamp),
+                    quant8_words(w[12], w[13], w[14], w[15], s, rcp, noclamp));
 }
 
-__device__ __forceinline__ uint32_t quant8_u4(const uint4& v, float s, float rcp) {
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-  uint32_t packed = 0;
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const float2 f = __half22float2(h[e]);
-    const uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
-                                    : quant_pair_zero_scale(f.x, f.y);
-    packed |= ((cd | (cd >> 12)) & 0xFFu) << (8 * e);
-  }
-  return packed;
+__device__ __forceinline__ uint32_t quant8_u4(const uint4& v, float s, float rcp, bool noclamp) {
+  return quant8_words(v.x, v.y, v.z, v.w, s, rcp, noclamp);
 }
 
 // Row absmax across the CTA: warp shuffle, one slot per warp, one barrier.
@@ -187,6 +168,8 @@ __device__ __forceinline__ float scale_from_absmax(float a, float clip, __half* 
 // issued before the current row is reduced.
 __global__ void __launch_bounds__(1024)
 quant_rows_kernel(const HadqParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float red[2][32];
   const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
   const int nchunks = p.n >> 3;
@@ -210,13 +193,14 @@ quant_rows_kernel(const HadqParams p) {
     const float a = block_absmax(amax, red[parity], lane, warp, nwarps);
     const float s = scale_from_absmax(a, p.clip, tid == 0 ? p.scales + row : nullptr);
     const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+    const bool noclamp = clamp_free(s, p.clip);
     uint32_t* qo = reinterpret_cast<uint32_t*>(p.q + row * (int64_t)(p.n >> 1));
     uint4* yo = p.y_out ? reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.y_out) + row * (int64_t)p.n) : nullptr;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int c = tid + j * T;
       if (c < nchunks) {
-        qo[c] = quant8_u4(cur[j], s, rcp);
+        qo[c] = quant8_u4(cur[j], s, rcp, noclamp);
         if (yo) yo[c] = cur[j];
       }
     }
@@ -235,6 +219,8 @@ __host__ __device__ constexpr int hadq_max_threads(int KT) {
 template <int KT>
 __global__ void __launch_bounds__(hadq_max_threads(KT))
 hadq_fast_kernel(const HadqParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x;
   const int nthreads = blockDim.x;
@@ -421,7 +407,7 @@ hadq_fast_kernel(const HadqParams p) {
       const float s = scale_from_absmax(a, p.clip, tid == 0 ? p.scales + row : nullptr);
       const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
       if (tid < ngroups)
-        *reinterpret_cast<uint4*>(p.q + row * (int64_t)(n >> 1) + tid * 16) = quant32(h, s, rcp);
+        *reinterpret_cast<uint4*>(p.q + row * (int64_t)(n >> 1) + tid * 16) = quant32(h, s, rcp, clamp_free(s, p.clip));
     } else {
       __syncthreads();   // the row buffer is rewritten by the next row
     }
@@ -436,6 +422,8 @@ template <> __device__ __forceinline__ float load_as_float<float>(const float* p
 template <typename T>
 __global__ void __launch_bounds__(256)
 hadq_generic_kernel(const HadqParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int n = p.n, K = p.K, m = p.m;
@@ -532,8 +520,8 @@ static int launch_fast(const HadqParams& p, int threads, size_t smem, cudaStream
     QR_CUDA(cudaFuncSetAttribute(hadq_fast_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 64) configured[dev] = smem;
   }
-  hadq_fast_kernel<KT><<<persistent_grid(p.rows, threads, smem), threads, smem, st>>>(p);
-  QR_LAUNCH_CHECK("hadq_fast_kernel");
+  QR_CUDA(launch_kernel(hadq_fast_kernel<KT>, dim3(persistent_grid(p.rows, threads, smem)), dim3(threads), smem, st,
+                        tuning("pdl", 0) != 0, p));
   return QR_OK;
 }
 
@@ -553,8 +541,7 @@ static int launch_generic(const HadqParams& p, cudaStream_t st) {
   if (per_sm < 1) per_sm = 1;
   int64_t grid = (int64_t)num_sms() * per_sm;
   if (grid > p.rows) grid = p.rows;
-  hadq_generic_kernel<T><<<(int)grid, 256, smem, st>>>(p);
-  QR_LAUNCH_CHECK("hadq_generic_kernel");
+  QR_CUDA(launch_kernel(hadq_generic_kernel<T>, dim3((int)grid), dim3(256), smem, st, tuning("pdl", 0) != 0, p));
   return QR_OK;
 }
 
@@ -596,8 +583,8 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
                        (!y_out || aligned16(y_out)) && (!do_quant || aligned16(q)) && n <= 32768;
   if (base_ok && K == 0 && do_quant && n >= 64) {
     int threads = ((n / 8 + 3) / 4 + 31) / 32 * 32;
-    quant_rows_kernel<<<persistent_grid(rows, threads, 1024), threads, 0, st>>>(p);
-    QR_LAUNCH_CHECK("quant_rows_kernel");
+    QR_CUDA(launch_kernel(quant_rows_kernel, dim3(persistent_grid(rows, threads, 1024)), dim3(threads), 0, st,
+                          tuning("pdl", 0) != 0, p));
     return QR_OK;
   }
   if (base_ok && K > 1 && m == 64 && ldx == n && tuning("hadq_tc", 1) != 0) {

@@ -88,6 +88,8 @@ __device__ __forceinline__ void fwht_regs_tc(float (&v)[N]) {
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -253,19 +255,12 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
         if (ew == 0 && lane == 0) p.scales[row] = sh;
         if (active) {
           const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+          const bool noclamp = clamp_free(s, p.clip);
+          const uint32_t* hw = reinterpret_cast<const uint32_t*>(h);
           uint32_t w4[8];
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            uint32_t packed = 0;
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const float2 f = __half22float2(h[4 * g + e]);
-              const uint32_t cd = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
-                                              : quant_pair_zero_scale(f.x, f.y);
-              packed |= ((cd | (cd >> 12)) & 0xFFu) << (8 * e);
-            }
-            w4[g] = packed;
-          }
+          for (int g = 0; g < 8; ++g)
+            w4[g] = quant8_words(hw[4 * g], hw[4 * g + 1], hw[4 * g + 2], hw[4 * g + 3], s, rcp, noclamp);
           uint4* qo = reinterpret_cast<uint4*>(p.q + row * (int64_t)(n >> 1) + kprime * 32);
           qo[0] = make_uint4(w4[0], w4[1], w4[2], w4[3]);
           qo[1] = make_uint4(w4[4], w4[5], w4[6], w4[7]);
@@ -332,8 +327,7 @@ int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k,
   }
   int64_t grid = num_sms();
   if (grid > rows) grid = rows;
-  hadq_tc_kernel<<<(int)grid, kTcThreads, smem, st>>>(tm, p);
-  QR_LAUNCH_CHECK("hadq_tc_kernel");
+  QR_CUDA(launch_kernel(hadq_tc_kernel, dim3((int)grid), dim3(kTcThreads), (size_t)smem, st, tuning("pdl", 0) != 0, tm, p));
   return QR_OK;
 }
 

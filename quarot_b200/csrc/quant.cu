@@ -5,19 +5,9 @@
 
 namespace qr {
 
-// Eight fp16 values (one uint4) -> four packed bytes.
+// Eight fp16 values (one uint4) -> four packed bytes (caller-provided scale: always clamped).
 __device__ __forceinline__ uint32_t quant8(const uint4& v, float s, float rcp) {
-  const __half2* h = reinterpret_cast<const __half2*>(&v);
-  uint32_t out = 0;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __half22float2(h[i]);
-    uint32_t c = (s != 0.0f) ? quant_pair(div_by_scale(f.x, s, rcp), div_by_scale(f.y, s, rcp))
-                             : quant_pair_zero_scale(f.x, f.y);
-    // c: code(2i) in bits 3:0, code(2i+1) in bits 19:16  ->  byte i = lo | hi << 4
-    out |= ((c & 0xF) | ((c >> 12) & 0xF0)) << (8 * i);
-  }
-  return out;
+  return quant8_words(v.x, v.y, v.z, v.w, s, rcp, false);
 }
 
 __global__ void __launch_bounds__(256)
@@ -104,6 +94,35 @@ static int grid_for(int64_t total_threads) {
   return (int)(blocks < cap ? blocks : cap);
 }
 
+// Self-test of the division shortcut: for every finite fp16 value x and every finite non-zero fp16 scale s,
+// the int4 code obtained from x * RN(1/s) must equal the one obtained from IEEE division.
+__device__ unsigned long long g_div_mismatch = 0;
+
+__global__ void __launch_bounds__(256)
+division_check_kernel(unsigned long long* mismatch) {
+  // blockIdx.x enumerates the scale bit patterns 0x0001 .. 0x7BFF (positive; the sign of s only flips the quotient)
+  const uint32_t sbits = blockIdx.x + 1;
+  const __half sh = __ushort_as_half((unsigned short)sbits);
+  const float s = __half2float(sh);
+  const float rcp = __frcp_rn(s);
+  unsigned int bad = 0;
+  for (uint32_t xb = threadIdx.x; xb < 65536u; xb += blockDim.x) {
+    if ((xb & 0x7C00u) == 0x7C00u) continue;   // inf / NaN inputs are outside the contract
+    const float x = __half2float(__ushort_as_half((unsigned short)xb));
+    const uint32_t fast = quant_pair(x * rcp, -x * rcp);
+    const uint32_t ieee = quant_pair(__fdiv_rn(x, s), __fdiv_rn(-x, s));
+    bad += (fast != ieee);
+    // the unclamped form is used when |x / s| <= 7.004
+    if (fabsf(__fdiv_rn(x, s)) <= 7.25f) {
+      const __half2 xx = __halves2half2(__ushort_as_half((unsigned short)xb), __ushort_as_half((unsigned short)(xb ^ 0x8000u)));
+      const uint32_t u = quant2_word<false>(*reinterpret_cast<const uint32_t*>(&xx), rcp);
+      const uint32_t codes = (u & 0xFu) | ((u >> 12) & 0xF0u);
+      bad += (codes != ((ieee & 0xFu) | ((ieee >> 12) & 0xF0u)));
+    }
+  }
+  if (bad) atomicAdd(mismatch, (unsigned long long)bad);
+}
+
 }  // namespace qr
 
 extern "C" {
@@ -141,6 +160,20 @@ int qr_sym_dequant_i32_f16(const int32_t* q, const void* scale_row, const void* 
         q, (const __half*)scale_row, (const __half*)scale_col, rows, cols, (__half*)out);
   }
   QR_LAUNCH_CHECK("qr_sym_dequant_i32_f16");
+  return QR_OK;
+}
+
+int qr_debug_division_check(uint64_t* mismatches_out) {
+  if (!mismatches_out) return qr::fail(QR_EINVAL, "qr_debug_division_check: null output");
+  unsigned long long* dptr = nullptr;
+  QR_CUDA(cudaGetSymbolAddress((void**)&dptr, qr::g_div_mismatch));
+  QR_CUDA(cudaMemset(dptr, 0, sizeof(unsigned long long)));
+  qr::division_check_kernel<<<0x7BFF, 256>>>(dptr);
+  QR_LAUNCH_CHECK("division_check_kernel");
+  QR_CUDA(cudaDeviceSynchronize());
+  unsigned long long v = 0;
+  QR_CUDA(cudaMemcpy(&v, dptr, sizeof(v), cudaMemcpyDeviceToHost));
+  *mismatches_out = (uint64_t)v;
   return QR_OK;
 }
 

@@ -153,6 +153,31 @@ def test_fused_hadamard_quant_bit_exact_given_own_hadamard(n, K, rows, clip):
     assert none is None and torch.equal(q2.cpu(), q) and torch.equal(_bits(s2), _bits(s))
 
 
+def test_division_by_reciprocal_gives_ieee_codes_for_every_fp16_pair():
+    """The quantisers multiply by RN(1/s) instead of dividing; the library checks all finite fp16 x against
+    all finite non-zero fp16 s on the device and reports how many int4 codes differ from IEEE division."""
+    import ctypes
+    bad = ctypes.c_uint64(123)
+    _lib.check(_lib.lib.qr_debug_division_check(ctypes.byref(bad)), "qr_debug_division_check")
+    assert bad.value == 0
+
+
+@pytest.mark.parametrize("n,K", [(4096, 0), (4096, 1), (11008, 0), (11008, 172), (28672, 28)])
+@pytest.mark.parametrize("magnitude", [2.0 ** -22, 2.0 ** -15, 1.0, 3000.0])
+def test_fused_quant_ties_and_tiny_scales(n, K, magnitude):
+    """Rows built from half-integer multiples of a power of two hit round-half-even ties; tiny magnitudes push
+    the scale into the subnormal fp16 range, where the code clamp matters; clip < 1 saturates."""
+    g = torch.Generator().manual_seed(n + K)
+    x = (torch.randint(-14, 15, (6, n), generator=g).float() * 0.5 * magnitude).half()
+    table = FH.device_table(K, DEV) if K > 1 else None
+    for clip in (1.0, 0.7):
+        q, s, y = qb.hadamard_quant(x.to(DEV), table, K, clip, return_y=True)
+        q, s, y = q.cpu(), s.cpu(), y.cpu()
+        s_ref = O.quantizer_scales(y, clip)
+        assert torch.equal(_bits(s), _bits(s_ref))
+        assert torch.equal(q, O.pack_i4(O.sym_quant_codes(y, s_ref)))
+
+
 def test_fused_quant_edge_rows():
     x = torch.zeros(4, 4096, dtype=torch.float16)
     x[1, 5] = 7.0            # scale exactly 1
