@@ -62,6 +62,9 @@ int num_sms() {
   return n;
 }
 
+static void* g_trace_ptr = nullptr;   // set through qr_debug_set_trace (debugging aid)
+void* debug_trace_ptr() { return g_trace_ptr; }
+
 static std::mutex g_tune_mu;
 static std::map<std::string, int> g_tune;
 
@@ -92,9 +95,14 @@ int qr_kernel_status(int* status_out) {
   return QR_OK;
 }
 
+int qr_debug_set_trace(void* device_buffer) {
+  qr::g_trace_ptr = device_buffer;
+  return QR_OK;
+}
+
 int qr_set_tuning(const char* key, int value) {
   static const char* known[] = {"gemm_bn", "gemm_pst", "gemm_ist", "gemm_acc", "gemm_grid",
-                                "gemm_swap_max_m", "gemm_splitk", "gemm_2sm", "gemm_ts", "gemm_sync", "gemm_debug", "gemm_tma_out", "pdl", "hadq_path", "hadq_tc", nullptr};
+                                "gemm_swap_max_m", "gemm_splitk", "gemm_2sm", "gemm_ts", "gemm_sync", "gemm_debug", "gemm_tma_out", "pdl", "hadq_debug", "hadq_path", "hadq_tc", nullptr};
   if (!key) return qr::fail(QR_EINVAL, "qr_set_tuning: null key");
   for (int i = 0; known[i]; ++i) {
     if (strcmp(known[i], key) == 0) {

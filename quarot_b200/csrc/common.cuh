@@ -17,6 +17,7 @@ int cuda_fail(cudaError_t e, const char* what);
 int* kernel_status_ptr();        // device address of the per-device status word (lazy, no allocation)
 int num_sms();
 int tuning(const char* key, int dflt);
+void* debug_trace_ptr();   // device buffer for clock64 time lines of a kernel, or null (debugging aid)
 
 #define QR_CUDA(expr)                                            \
   do {                                                           \

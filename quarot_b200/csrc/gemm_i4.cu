@@ -535,31 +535,34 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           mine_in_tile = true;
           const int s = it % IST;
           const uint32_t ph = (it / IST) & 1;
+          // the operand descriptors do not depend on the hand-over: they are ready before the waits
+          const uint32_t a_lo = desc_lo(smem_base + L::kI8Off + s * L::kI8Stage);
+          const uint32_t b_lo = a_lo + ((kBM * 128) >> 4);
           if (kb < 2) {   // first block of this thread in the tile: the accumulator buffer must have been drained
             if (!mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 12)) { ok = false; break; }
           }
           if (!mbar_wait(full_i(s), ph, abort_flag, p.status, 13)) { ok = false; break; }
           // my turn?
           {
-            const long long t0 = clock64();
             bool got = (*turn == it);
-            for (uint32_t spin = 1; !got; ++spin) {
-              got = (*turn == it);
-              if (!got && (spin & 255u) == 0u) {
-                if (*abort_flag) break;
-                if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(p.status, 17); break; }
+            if (!got) {
+              const long long t0 = clock64();
+              for (uint32_t spin = 1; !got; ++spin) {
+                got = (*turn == it);
+                if (!got && (spin & 255u) == 0u) {
+                  if (*abort_flag) break;
+                  if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(p.status, 17); break; }
+                }
               }
             }
             if (!got) { ok = false; break; }
           }
+          // critical section of the main loop: nothing but the fences, the four MMAs and the hand-over
           tc_fence_after();
-          stamp(0, it, 1);
-          const uint32_t a_addr = smem_base + L::kI8Off + s * L::kI8Stage;
-          const uint64_t da = make_kmajor_sw128_desc(a_addr);
-          const uint64_t db = make_kmajor_sw128_desc(a_addr + kBM * 128);
-#pragma unroll
-          for (int k4 = 0; k4 < 4; ++k4)
-            umma_i8_2sm(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+          umma_i8_2sm_w<-1>(d_tmem, a_lo, b_lo, kDescHiKmajorSw128, idesc, kb != 0 ? 1u : 0u);
+          umma_i8_2sm_w<1>(d_tmem, a_lo + 2, b_lo + 2, kDescHiKmajorSw128, idesc);   // +32 bytes along K = +2 in the address field
+          umma_i8_2sm_w<1>(d_tmem, a_lo + 4, b_lo + 4, kDescHiKmajorSw128, idesc);
+          umma_i8_2sm_w<1>(d_tmem, a_lo + 6, b_lo + 6, kDescHiKmajorSw128, idesc);
           tc_fence_before();
           *turn = it + 1;
           stamp(0, it, 2);
@@ -1365,7 +1368,6 @@ static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t*
   return splits;
 }
 
-static void* g_trace_ptr = nullptr;   // set through qr_debug_set_trace (debugging aid)
 
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
@@ -1390,7 +1392,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   p.splits = 1; p.ws_partial = nullptr; p.ws_counter = nullptr;
   p.sync_mode = tuning("gemm_sync", 7);
   p.debug = tuning("gemm_debug", 0);
-  p.trace = reinterpret_cast<long long*>(g_trace_ptr);
+  p.trace = reinterpret_cast<long long*>(debug_trace_ptr());
   p.bias = reinterpret_cast<const __half*>(bias);
   p.tma_out = 0;
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
@@ -1473,11 +1475,6 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
                      int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16", A, B, M, N, K, out, ldo, sA, sB, bias,
                                     (cudaStream_t)stream);
-}
-
-int qr_debug_set_trace(void* device_buffer) {
-  qr::g_trace_ptr = device_buffer;
-  return QR_OK;
 }
 
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {

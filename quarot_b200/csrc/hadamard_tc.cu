@@ -6,13 +6,16 @@
 //
 // One persistent CTA per SM.  hadK (padded to 128-row tiles and 64-column swizzle atoms) is
 // written once into shared memory as the K-major A operand.  A token row is 172 rows of 128 bytes,
-// i.e. already the MN-major B operand [k][m]: TMA copies it with the 128-byte swizzle into a ring
-// of three buffers and the MMA warp issues ceil(K/16) MMAs per 128-row tile of hadK.  Thread k' of
-// the epilogue warps reads its 64 accumulators with tcgen05.ld, runs the 6 butterfly stages in
+// i.e. already the MN-major B operand [k][m].  The unit of work is a PAIR of consecutive token rows:
+// TMA copies both with the 128-byte swizzle into one stage of a two-stage ring, and the MMA warp issues
+// ceil(K/16) MMAs of N = 128 (two 64-column atoms, one per token row) per 128-row tile of hadK,
+// alternating between the tiles so that two independent accumulation chains are in flight (short MMAs
+// chained on one accumulator run at the latency of the tensor pipe, not at its throughput).
+// Thread k' of an epilogue warp reads its 64 accumulators with tcgen05.ld, runs the 6 butterfly stages in
 // registers (no shuffles, no shared memory), scales, rounds to fp16, joins the row-wide absmax
-// (per-warp slots published through a bounded mbarrier), quantises with torch's division arithmetic and stores 32 packed bytes.
-// Accumulators are double buffered and two sets of epilogue warps take alternate token rows, so the
-// MMAs of row i+1 and the epilogue of row i-1 overlap the epilogue of row i.
+// (per-warp slots published through a bounded mbarrier), quantises with torch's division arithmetic and
+// stores 32 packed bytes.  Two sets of epilogue warps take the two rows of a pair; accumulators are
+// double buffered, so the MMAs of pair i+1 overlap the epilogue of pair i.
 //
 // All mbarrier waits are bounded (see tc_ptx.cuh); on a timeout the CTA sets the device status
 // word, leaves its loops, frees tensor memory and returns.
@@ -37,11 +40,13 @@ struct HadqTcParams {
   __half* y_out;
   int do_quant;
   int* status;
+  long long* trace;   // optional clock64 time line of CTA 0 (debugging aid), or null
+  int debug;          // timing experiments only (results become wrong): 1 = skip the second hadK tile, 2 = 4 k steps only
 };
 
-constexpr int kTcEpiWarps = 8;        // epilogue warps per set; two sets take alternate token rows
+constexpr int kTcEpiWarps = 8;        // epilogue warps per set; set r takes row r of every pair of token rows
 constexpr int kTcThreads = 32 * (2 + 2 * kTcEpiWarps);
-constexpr int kTcNB = 3;              // token-row buffers
+constexpr int kTcNB = 2;              // ring stages, each holding a pair of token rows
 constexpr int kTcNumBars = 2 * kTcNB + 4 + 2;   // full_b, empty_b, acc_full[2], acc_empty[2], red_bar[2]
 
 __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -51,6 +56,32 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+
+// The same MMA with the operand descriptors as (low word, shared high word), see tc_ptx.cuh.  ACC = 1 accumulates,
+// ACC = -1 takes the decision from `accumulate` at run time.
+template <int ACC>
+__device__ __forceinline__ void umma_f16_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                           uint32_t accumulate = 1u) {
+  if (ACC < 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(ACC)
+        : "memory");
+  }
 }
 
 // MN-major operand, 128-byte swizzle: 64 contiguous elements along MN per row, rows are K;
@@ -90,16 +121,17 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
   pdl_launch_dependents();
   pdl_wait();
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[512 + 7 * 64 + 2] = clock64();
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // layout: [A: KA atoms x (MT*128 rows x 128 B)][B ring][barriers][tmem slot][abort][reduction slots]
+  // layout: [A: KA atoms x (MT*128 rows x 128 B)][B ring: kTcNB stages x 2 token rows][barriers][tmem slot][abort][reduction slots]
   const int a_atom_bytes = p.MT * 128 * 128;
   const int a_bytes = p.KA * a_atom_bytes;
   const uint32_t b_off = (uint32_t)a_bytes;
-  const uint32_t bar_off = b_off + kTcNB * p.b_bytes;
+  const uint32_t bar_off = b_off + 2 * kTcNB * p.b_bytes;
   const uint32_t bar_base = smem_base + bar_off;
   auto full_b = [&](int s) { return bar_base + 8u * s; };
   auto empty_b = [&](int s) { return bar_base + 8u * (kTcNB + s); };
@@ -108,108 +140,171 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
   auto red_bar = [&](int b) { return bar_base + 8u * (2 * kTcNB + 4 + b); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + bar_off + 8 * kTcNumBars);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + bar_off + 8 * kTcNumBars + 8);
-  volatile float* red = reinterpret_cast<volatile float*>(smem_gen + bar_off + 8 * kTcNumBars + 16);   // [2][kTcEpiWarps]
+  volatile float* red = reinterpret_cast<volatile float*>(smem_gen + bar_off + 8 * kTcNumBars + 16);   // [2 sets][2][kTcEpiWarps]
 
-  // ---- one-time set-up: hadK -> swizzled K-major A tiles (zero padded), zero the k padding rows of B
-  {
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kTcNB; ++s) { mbar_init(full_b(s), 1); mbar_init(empty_b(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), 2 * kTcEpiWarps); mbar_init(red_bar(a), kTcEpiWarps); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  constexpr uint32_t kTmemCols = 512;   // 2 pair buffers x 2 tiles x (2 rows x 64 columns)
+  if (warp == 1) {
+    tmem_alloc(smem_base + bar_off + 8 * kTcNumBars, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // time line of CTA 0: [set][phase 0..7][pair index < 64]
+  auto stamp = [&](int set_, int phase, uint32_t i_) {
+    if (p.trace && blockIdx.x == 0 && i_ < 64) p.trace[set_ * 512 + phase * 64 + i_] = clock64();
+  };
+  const int64_t npairs = (p.rows + 1) >> 1;
+
+  if (warp != 0) {
+    // ---- one-time set-up by all warps but the producer (which already streams token rows in):
+    // hadK -> swizzled K-major A tiles (zero padded), zero the k padding rows of the token-row buffers
+    const int t = threadIdx.x - 32, nt = kTcThreads - 32;
     const int rows = p.MT * 128, K = p.K;
     const int chunks = rows * p.KA * 8;                       // 16-byte chunks of the A operand
-    for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
-      const int ka = c / (rows * 8);
-      const int rem = c - ka * rows * 8;
-      const int r = rem >> 3, ch = rem & 7;
-      uint4 v = make_uint4(0, 0, 0, 0);
-      const int c0 = ka * 64 + ch * 8;                        // first hadK column of this chunk
-      if (r < K && c0 < K) {
-        __align__(16) __half tmp[8];
+    const bool vec = (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.had_k) & 7) == 0);
+    // four chunks per thread and round: the loads of a round are issued before its stores
+    for (int c_base = t; c_base < chunks; c_base += 4 * nt) {
+      uint4 v[4];
+      uint32_t dst[4];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) tmp[e] = (c0 + e < K) ? p.had_k[(size_t)r * K + c0 + e] : __float2half(0.0f);
-        v = *reinterpret_cast<const uint4*>(tmp);
+      for (int u = 0; u < 4; ++u) {
+        const int c = c_base + u * nt;
+        v[u] = make_uint4(0, 0, 0, 0);
+        dst[u] = 0xFFFFFFFFu;
+        if (c < chunks) {
+          const int ka = c / (rows * 8);
+          const int rem = c - ka * rows * 8;
+          const int r = rem >> 3, ch = rem & 7;
+          const int c0 = ka * 64 + ch * 8;                      // first hadK column of this chunk
+          dst[u] = (uint32_t)(ka * a_atom_bytes + r * 128 + ((ch ^ (r & 7)) << 4));
+          if (r < K && c0 < K) {
+            const __half* src = p.had_k + (size_t)r * K + c0;
+            if (vec) {      // K % 4 == 0: the chunk starts on an 8-byte boundary and holds 4 or 8 valid columns
+              const uint2 lo = __ldg(reinterpret_cast<const uint2*>(src));
+              uint2 hi = make_uint2(0, 0);
+              if (c0 + 8 <= K) hi = __ldg(reinterpret_cast<const uint2*>(src + 4));
+              v[u] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+            } else {
+              __align__(16) __half tmp[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) tmp[e] = (c0 + e < K) ? src[e] : __float2half(0.0f);
+              v[u] = *reinterpret_cast<const uint4*>(tmp);
+            }
+          }
+        }
       }
-      *reinterpret_cast<uint4*>(smem_gen + ka * a_atom_bytes + r * 128 + ((ch ^ (r & 7)) << 4)) = v;
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (dst[u] != 0xFFFFFFFFu) *reinterpret_cast<uint4*>(smem_gen + dst[u]) = v[u];
     }
     const int pad_rows = p.KT16 * 16 - K;
-    for (int c = threadIdx.x; c < kTcNB * pad_rows * 8; c += blockDim.x) {
+    for (int c = t; c < 2 * kTcNB * pad_rows * 8; c += nt) {
       const int s = c / (pad_rows * 8);
       const int rem = c - s * pad_rows * 8;
       *reinterpret_cast<uint4*>(smem_gen + b_off + s * p.b_bytes + (K + (rem >> 3)) * 128 + ((rem & 7) << 4)) =
           make_uint4(0, 0, 0, 0);
     }
+    fence_proxy_async_smem();   // A tiles and zeroed padding were written with ordinary stores
+    asm volatile("bar.sync 1, %0;" ::"n"(kTcThreads - 32) : "memory");
+    if (threadIdx.x == 32) stamp(1, 7, 0);
   }
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kTcNB; ++s) { mbar_init(full_b(s), 1); mbar_init(empty_b(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), kTcEpiWarps); mbar_init(red_bar(a), kTcEpiWarps); }
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  constexpr uint32_t kTmemCols = 256;   // 2 row buffers x 2 tiles x 64 columns
-  if (warp == 1) {
-    tmem_alloc(smem_base + bar_off + 8 * kTcNumBars, kTmemCols);
-    tmem_relinquish();
-  }
-  fence_proxy_async_smem();   // A tiles and zeroed padding were written with ordinary stores
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer: one token row per buffer
+    // ------------------------------------------------------------ TMA producer: a pair of token rows per stage
     if (lane == 0) {
       uint32_t i = 0;
-      for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, ++i) {
+      for (int64_t pair = blockIdx.x; pair < npairs; pair += gridDim.x, ++i) {
         const int s = i % kTcNB;
         if (!mbar_wait(empty_b(s), ((i / kTcNB) & 1) ^ 1, abort_flag, p.status, 31)) break;
-        mbar_expect_tx(full_b(s), (uint32_t)p.K * 128u);
-        tma_load_2d(smem_base + b_off + s * p.b_bytes, &tmX, full_b(s), 0, (int)(row * p.K));
+        stamp(0, 7, i);
+        const bool two = 2 * pair + 1 < p.rows;
+        mbar_expect_tx(full_b(s), (uint32_t)p.K * 128u * (two ? 2u : 1u));
+        const uint32_t dst = smem_base + b_off + (2 * s) * p.b_bytes;
+        tma_load_2d(dst, &tmX, full_b(s), 0, (int)(2 * pair * p.K));
+        if (two) tma_load_2d(dst + p.b_bytes, &tmX, full_b(s), 0, (int)((2 * pair + 1) * p.K));
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16_kmn(128, 64);
+      constexpr uint32_t idesc = make_idesc_f16_kmn(128, 128);
       uint32_t i = 0;
-      for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, ++i) {
+      for (int64_t pair = blockIdx.x; pair < npairs; pair += gridDim.x, ++i) {
         const int s = i % kTcNB, a = i & 1;
         if (!mbar_wait(full_b(s), (i / kTcNB) & 1, abort_flag, p.status, 32)) break;
         if (!mbar_wait(acc_empty(a), ((i >> 1) & 1) ^ 1, abort_flag, p.status, 33)) break;
         tc_fence_after();
-        const uint32_t b_addr = smem_base + b_off + s * p.b_bytes;
-        for (int mt = 0; mt < p.MT; ++mt) {
-          const uint32_t d_tmem = tmem_base + a * 128 + mt * 64;
-          for (int j = 0; j < p.KT16; ++j) {
-            const uint32_t a_addr = smem_base + (j >> 2) * a_atom_bytes + mt * (128 * 128) + (j & 3) * 32;
-            const uint64_t da = make_kmajor_sw128_desc(a_addr);
-            const uint64_t db = make_mnmajor_sw128_desc(b_addr + j * 2048, (uint32_t)p.b_bytes, 1024);
-            umma_f16(d_tmem, da, db, idesc, j != 0 ? 1u : 0u);
+        stamp(0, 6, i);
+        // Lean issue loop (one thread; every dependent integer instruction costs several cycles): descriptors are
+        // (low word, constant high word) pairs advanced by 32-bit adds.  A: k step = +32 bytes inside a 64-column
+        // atom, next atom a_atom_bytes further, second hadK tile 16 KB further.  B: k step = 16 rows of 128 bytes;
+        // its low word also carries the distance between the two token rows (leading byte offset).
+        const int kt_n = (p.debug & 2) ? 4 : p.KT16;
+        const bool two_tiles = p.MT > 1 && !(p.debug & 1);
+        const uint32_t d0 = tmem_base + a * 256;
+        uint32_t a_lo = desc_lo(smem_base);
+        uint32_t b_lo = desc_lo(smem_base + b_off + (2 * s) * p.b_bytes) | ((((uint32_t)p.b_bytes >> 4) & 0x3FFFu) << 16);
+        const uint32_t a_atom_step = (uint32_t)a_atom_bytes >> 4;
+        int j = 0;
+        for (int ja = 0; ja < p.KA; ++ja, a_lo += a_atom_step, b_lo += 4 * 128) {
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj, ++j) {
+            if (j < kt_n) {
+              if (jj == 0) {
+                umma_f16_w<-1>(d0, a_lo, b_lo, kDescHiKmajorSw128, idesc, ja != 0 ? 1u : 0u);
+                if (two_tiles) umma_f16_w<-1>(d0 + 128, a_lo + 1024, b_lo, kDescHiKmajorSw128, idesc, ja != 0 ? 1u : 0u);
+              } else {
+                umma_f16_w<1>(d0, a_lo + 2 * jj, b_lo + 128 * jj, kDescHiKmajorSw128, idesc);
+                if (two_tiles) umma_f16_w<1>(d0 + 128, a_lo + 2 * jj + 1024, b_lo + 128 * jj, kDescHiKmajorSw128, idesc);
+              }
+            }
           }
         }
+        stamp(0, 6, 32 + i);
         umma_commit(empty_b(s));
         umma_commit(acc_full(a));
       }
     }
   } else {
     // ------------------------------------------------------------ epilogue: thread = output row k'
-    const int set = (warp - 2) >> 3;           // set 0 drains accumulator buffer 0 (even rows), set 1 buffer 1
+    const int set = (warp - 2) >> 3;           // set r handles row r of every pair
     const int ew = (warp - 2) & 7;
     const int mt = ew >> 2, q4 = warp & 3;
     const int kprime = mt * 128 + q4 * 32 + lane;
     const bool warp_active = (mt * 128 + q4 * 32) < p.K && mt < p.MT;
     const bool active = kprime < p.K && mt < p.MT;
     const int n = p.K * 64;
-    uint32_t i = set;
-    for (int64_t row = blockIdx.x + (int64_t)set * gridDim.x; row < p.rows; row += 2 * (int64_t)gridDim.x, i += 2) {
+    uint32_t i = 0;
+    for (int64_t pair = blockIdx.x; pair < npairs; pair += gridDim.x, ++i) {
       const int a = i & 1;
+      const int64_t row = 2 * pair + set;
       __half2 h[32];
       float amax = 0.0f;
+      const bool st = (ew == 0 && lane == 0);
+      if (st) stamp(set, 0, i);
       bool ok = mbar_wait(acc_full(a), (i >> 1) & 1, abort_flag, p.status, 34);
       if (!ok) break;
       tc_fence_after();
+      if (st) stamp(set, 1, i);
+      if (row >= p.rows) {      // odd row count: the last pair has no second row
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty(a));
+        continue;
+      }
       if (warp_active) {
         float v[64];
         {
           uint32_t r[32];
-          const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * 128 + mt * 64);
+          const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * 256 + mt * 128 + set * 64);
           tmem_ld32(taddr, r);
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(r[e]);
@@ -220,6 +315,7 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty(a));
+        if (st) stamp(set, 2, i);
         fwht_regs_tc<64>(v);
         __half2 mx = __float2half2_rn(0.0f);
 #pragma unroll
@@ -239,13 +335,17 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
       } else {
         if (lane == 0) mbar_arrive(acc_empty(a));
       }
+      if (st) stamp(set, 3, i);
       if (p.do_quant) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
         // row-wide absmax: one slot per warp, published through a (bounded) mbarrier
-        volatile float* slots = red + (i & 1) * kTcEpiWarps;
-        if (lane == 0) { slots[ew] = amax; mbar_arrive(red_bar(i & 1)); }
-        if (!mbar_wait(red_bar(i & 1), (i >> 1) & 1, abort_flag, p.status, 35)) break;
+        // each set has its own barrier; the slots alternate between pairs so that a fast warp cannot overwrite
+        // a value that a slow warp of the same set has not read yet
+        volatile float* slots = red + (set * 2 + (i & 1)) * kTcEpiWarps;
+        if (lane == 0) { slots[ew] = amax; mbar_arrive(red_bar(set)); }
+        if (!mbar_wait(red_bar(set), i & 1, abort_flag, p.status, 35)) break;
+        if (st) stamp(set, 4, i);
         float amx = 0.0f;
 #pragma unroll
         for (int w = 0; w < kTcEpiWarps; ++w) amx = fmaxf(amx, slots[w]);
@@ -266,11 +366,13 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
           qo[1] = make_uint4(w4[4], w4[5], w4[6], w4[7]);
         }
       }
+      if (st) stamp(set, 5, i);
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) stamp(1, 7, 1);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -315,8 +417,10 @@ int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k,
   p.scale = (float)(1.0 / sqrt((double)n)); p.clip = clip; p.q = q;
   p.scales = reinterpret_cast<__half*>(scales); p.y_out = reinterpret_cast<__half*>(y_out);
   p.do_quant = do_quant; p.status = status;
+  p.trace = reinterpret_cast<long long*>(debug_trace_ptr());
+  p.debug = tuning("hadq_debug", 0);
   p.b_bytes = (p.KT16 * 16 * 128 + 1023) & ~1023;
-  const int smem = p.KA * p.MT * 128 * 128 + kTcNB * p.b_bytes + 8 * kTcNumBars + 16 + 2 * kTcEpiWarps * 4 + 1024 + 64;
+  const int smem = p.KA * p.MT * 128 * 128 + 2 * kTcNB * p.b_bytes + 8 * kTcNumBars + 16 + 4 * kTcEpiWarps * 4 + 1024 + 64;
   if (smem > 227 * 1024) return QR_EUNSUPPORTED;
   static thread_local int configured[64] = {0};
   int dev = 0;
@@ -326,7 +430,7 @@ int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k,
     if (dev < 64) configured[dev] = smem;
   }
   int64_t grid = num_sms();
-  if (grid > rows) grid = rows;
+  if (grid > (rows + 1) / 2) grid = (rows + 1) / 2;
   QR_CUDA(launch_kernel(hadq_tc_kernel, dim3((int)grid), dim3(kTcThreads), (size_t)smem, st, tuning("pdl", 0) != 0, tm, p));
   return QR_OK;
 }

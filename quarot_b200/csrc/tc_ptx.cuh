@@ -161,6 +161,13 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// The same descriptor as two 32-bit words.  Only the start-address field (low word) changes between the MMAs of
+// a tile, so an issuing thread keeps the constant high word and advances the low word with one 32-bit add per
+// operand instead of rebuilding 64-bit values: the MMA-issuing thread is a single thread whose dependent
+// integer instructions cost several cycles each, and those cycles are on the critical path of the main loop.
+constexpr uint32_t kDescHiKmajorSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return (smem_addr & 0x3FFFFu) >> 4; }
+
 // Instruction descriptor for kind::i8: signed 8-bit A and B, both K-major, int32 accumulate.
 __host__ __device__ constexpr uint32_t make_idesc_i8(int umma_m, int umma_n) {
   return (2u << 4)                       // D format: S32
@@ -236,6 +243,31 @@ __device__ __forceinline__ void umma_i8_2sm(uint32_t d_tmem, uint64_t a_desc, ui
       "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// cta_group::2 kind::i8 MMA with the operand descriptors given as (low word, shared high word).  ACC = 1:
+// accumulate into D; ACC = 0: overwrite D; ACC = -1: decided at run time by `accumulate`.
+template <int ACC>
+__device__ __forceinline__ void umma_i8_2sm_w(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc,
+                                              uint32_t accumulate = 1u) {
+  if (ACC < 0) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "n"(ACC)
+        : "memory");
+  }
 }
 // Arrives (once) on the mbarrier at shared::cluster address `bar` when all MMAs issued so far by this
 // thread have completed; `bar` may be this CTA's own barrier or the peer's (mapa_cluster).
