@@ -424,8 +424,23 @@ struct SmemLayout2 {
 
 constexpr int kWidenGroups2 = 3;                                  // widen groups of four warps, taking k-blocks round-robin
 constexpr int kWidenWarps2 = 4 * kWidenGroups2;
-constexpr int kIssuerBWarp = 2 + kEpiWarps + kWidenWarps2;        // warp index of the second MMA issuer
-constexpr int kThreads2 = 32 * (kIssuerBWarp + 1);
+// Warp roles.  A warp is served by the warp scheduler (id modulo 4) it was born on, and a scheduler shares its
+// issue slots evenly among its ready warps.  The two MMA issuers and the TMA producer are single threads whose
+// instruction latency is the critical path of the main loop, so scheduler 1 carries only them (warps 1, 5, 9),
+// one epilogue warp (13: the four epilogue warps must cover the four tensor-memory lane quarters, id modulo 4)
+// and an idle warp (17); the twelve widen warps, which issue continuously, live on schedulers 0, 2 and 3.
+constexpr int kIssuerAWarp = 1;
+constexpr int kIssuerBWarp = 5;
+constexpr int kProducerWarp2 = 9;
+constexpr int kThreads2 = 32 * 20;
+static_assert(kWidenWarps2 == 12, "widen_index2 enumerates twelve widen warps");
+__device__ __forceinline__ bool is_epilogue_warp2(int w) { return (w >= 2 && w <= 4) || w == 13; }
+// 0 .. 11 for the widen warps (0, 6-8, 10-12, 14-16, 18, 19), -1 otherwise
+__device__ __forceinline__ int widen_index2(int w) {
+  if (w == 0) return 0;
+  if (w < 6 || (w & 3) == 1) return -1;
+  return w - 5 - ((w - 5) >> 2);   // 6,7,8 -> 1,2,3; 10,11,12 -> 4,5,6; 14,15,16 -> 7,8,9; 18,19 -> 10,11
+}
 
 template <int PST, int IST, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
@@ -490,7 +505,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   const int num_clusters = gridDim.x >> 1;
   if (threadIdx.x == 0) stamp(0, 1, 7);
 
-  if (warp == 0) {
+  if (warp == kProducerWarp2) {
     // ------------------------------------------------------------ TMA producer (own rows only)
     if (lane == 0) {
       pdl_wait();   // operands may come from the preceding kernel
@@ -510,7 +525,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
       }
     }
-  } else if (warp == 1 || warp == kIssuerBWarp) {
+  } else if (warp == kIssuerAWarp || warp == kIssuerBWarp) {
     // ------------------------------------------------------------ MMA issuers (leader CTA only)
     // Issuing is the critical path of the main loop: per k-block one thread spends several hundred cycles in
     // the barrier wait, the four tcgen05.mma and the commit, more than the MMAs take to execute.  Two threads of
@@ -519,7 +534,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     // before/after_thread_sync (which orders the asynchronous MMAs of the two threads), and does its wait for
     // the next block and its commit while the other thread issues.
     if (leader && lane == 0) {
-      const int me = (warp == 1) ? 0 : 1;
+      const int me = (warp == kIssuerAWarp) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc_i8(2 * kBM, kBN2);
       const uint32_t peer_empty_i0 = mapa_cluster(empty_i(0), 1);
       const uint32_t peer_acc_full0 = mapa_cluster(acc_full(0), 1);
@@ -589,7 +604,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
       }
     }
-  } else if (warp < 2 + kEpiWarps) {
+  } else if (is_epilogue_warp2(warp)) {
     // ------------------------------------------------------------ epilogue (own 128 accumulator rows)
     // Warp q4 owns accumulator lanes 32 q4 .. 32 q4 + 31 (one output row per thread).  With a tensor map over
     // the output the rows are written as tiled stores: the warp converts 128 bytes of every row (64 fp16 or
@@ -731,12 +746,12 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
       if (q4 == 0) stamp(lane, 32 + tl, 7);
     }
     if (lane == 0) bulk_wait_read_all();   // the staging block must outlive the TMA unit's reads of it
-  } else if (warp < 2 + kEpiWarps + kWidenWarps2) {
+  } else if (widen_index2(warp) >= 0) {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
     // Groups of four warps take the k-blocks round-robin, so that a group has kWidenGroups2 MMA periods
     // per stage (its stores and the proxy fence take more than one).  Packed data is read into registers
     // before the int8 slot is waited for, which keeps the shared-memory read off the slot-reuse path.
-    const int wt = threadIdx.x - 32 * (2 + kEpiWarps);
+    const int wt = widen_index2(warp) * 32 + lane;
     const int group = wt >> 7;                          // four warps per group
     const int gt = wt & 127;                            // 0 .. 127 inside the group
     constexpr int kChunks = kRows2 * 4;                 // 1024 packed 16-byte chunks per stage
