@@ -613,6 +613,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     // and clips what lies outside the matrix.  The load/store pipe of the SM, which the widen warps saturate,
     // then sees 16 store wavefronts per block instead of 128 scattered 16-byte global stores.
     // The tile's 256 column scales (and bias) are fetched into shared memory before the accumulator is waited for.
+    // The scales are stored divided by 256: float(256 a) * (s_row * (s_col / 256)) rounds exactly like
+    // float(a) * (s_row * s_col), because scaling by a power of two commutes with every rounding involved.
     const int q4 = warp & 3;
     const int prow_in_tile = q4 * 32 + lane;
     const uint32_t leader_acc_empty0 = mapa_cluster(acc_empty(0), 0);
@@ -634,7 +636,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
 #pragma unroll
         for (int j = lane; j < kBN2; j += 32) {
           const int col = tq * kBN2 + j;
-          sqf[j] = col < p.rowsQ ? __half2float(p.sQ[col]) : 0.0f;
+          sqf[j] = col < p.rowsQ ? __half2float(p.sQ[col]) * 0.00390625f : 0.0f;   // 1/256: the accumulator is 256 x the dot product
           if (p.bias) bsh[j] = col < p.rowsQ ? p.bias[col] : __float2half(0.0f);
         }
         __syncwarp();
@@ -682,14 +684,14 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
                 const int jc = c0 + 32 * h + 8 * e;     // column inside the tile
                 const float4 s0 = *reinterpret_cast<const float4*>(sqf + jc);
                 const float4 s1 = *reinterpret_cast<const float4*>(sqf + jc + 4);
-                hh[0] = __floats2half2_rn((float)((int32_t)r[8 * e + 0] >> 8) * (sp * s0.x),
-                                          (float)((int32_t)r[8 * e + 1] >> 8) * (sp * s0.y));
-                hh[1] = __floats2half2_rn((float)((int32_t)r[8 * e + 2] >> 8) * (sp * s0.z),
-                                          (float)((int32_t)r[8 * e + 3] >> 8) * (sp * s0.w));
-                hh[2] = __floats2half2_rn((float)((int32_t)r[8 * e + 4] >> 8) * (sp * s1.x),
-                                          (float)((int32_t)r[8 * e + 5] >> 8) * (sp * s1.y));
-                hh[3] = __floats2half2_rn((float)((int32_t)r[8 * e + 6] >> 8) * (sp * s1.z),
-                                          (float)((int32_t)r[8 * e + 7] >> 8) * (sp * s1.w));
+                hh[0] = __floats2half2_rn((float)(int32_t)r[8 * e + 0] * (sp * s0.x),
+                                          (float)(int32_t)r[8 * e + 1] * (sp * s0.y));
+                hh[1] = __floats2half2_rn((float)(int32_t)r[8 * e + 2] * (sp * s0.z),
+                                          (float)(int32_t)r[8 * e + 3] * (sp * s0.w));
+                hh[2] = __floats2half2_rn((float)(int32_t)r[8 * e + 4] * (sp * s1.x),
+                                          (float)(int32_t)r[8 * e + 5] * (sp * s1.y));
+                hh[3] = __floats2half2_rn((float)(int32_t)r[8 * e + 6] * (sp * s1.z),
+                                          (float)(int32_t)r[8 * e + 7] * (sp * s1.w));
                 if (p.bias) {
                   const uint4 bb = *reinterpret_cast<const uint4*>(bsh + jc);
                   const __half2* bh = reinterpret_cast<const __half2*>(&bb);
