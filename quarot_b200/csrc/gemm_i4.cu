@@ -418,7 +418,7 @@ struct SmemLayout2 {
   static constexpr int kNumBars = 2 * PST + 2 * IST + 4;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
-  static constexpr int kTotal = kAbortOff + 8;
+  static constexpr int kTotal = kAbortOff + 16;   // abort flag, issuer turn, scratch word, loads issued
   static constexpr int kDynamic = kTotal + 1024;
 };
 
@@ -467,6 +467,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
   volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
+  // number of k-blocks whose TMA loads this CTA's producer has issued
+  volatile uint32_t* issued = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 12);
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
   pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
   if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[7 * 64 + 0] = clock64();   // life-cycle stamps live in slot 7
@@ -482,6 +484,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 2); mbar_init(acc_empty(a), 2 * kEpiWarps); }
     *abort_flag = 0;
     *turn = 0;
+    *reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 12) = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -522,6 +525,10 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
           tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * 2 * kBM + (int)rank * kBM);
           tma_load_2d(dst + kBM * kBKBytes, &tmQ, full_p(s), kb * kBKBytes, tq * kBN2 + (int)rank * (kBN2 / 2));
+          // No ordering with the barrier operations is needed: all that a reader relies on is that this thread has
+          // passed its empty_p wait for this slot, which precedes the store in program order, and a CTA's shared
+          // memory is a single copy.
+          *issued = it + 1;
         }
       }
     }
@@ -767,6 +774,25 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         if ((int)(it % kWidenGroups2) != group) continue;
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
+        // A group comes back to a staging slot only every third use of it (3 groups, 4 slots), and TMA loads may
+        // complete out of order: the load of the slot's PREVIOUS use (k-block it - 4, read by another group) may
+        // still be in flight when this group gets here, and a parity wait cannot tell "previous phase not finished"
+        // from "this phase finished" (seen on the GPU as a rare deadlock).  The producer therefore publishes how
+        // many loads it has issued; once the load of k-block `it` is issued (which needs the previous use
+        // consumed), the barrier is in this phase or has completed it, and the parity wait is unambiguous.
+        // (A plain volatile read is enough on this side: the barrier wait below is control-dependent on it.)
+        if (*issued <= it) {
+          const long long t0 = clock64();
+          bool got = false;
+          for (uint32_t spin = 1; !got; ++spin) {
+            got = (*issued > it);
+            if (!got && (spin & 255u) == 0u) {
+              if (*abort_flag) break;
+              if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(p.status, 18); break; }
+            }
+          }
+          if (!got) { ok = false; break; }
+        }
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
         if (gt == 0) stamp(0, it, 4);
         const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
@@ -1386,10 +1412,16 @@ static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t*
 }
 
 
+// A caller-provided workspace starts with a counter region of fixed size, whatever the shape: the kernels leave
+// their counters at zero, so calls of different shapes can share one workspace without the partial tiles of one
+// shape ever landing where another shape keeps its counters.  (The library's built-in scratch uses a compact
+// layout and is cleared before every call instead.)
+constexpr size_t kWsCounterRegion = 64u << 10;
+
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
-                    void* ws = nullptr, size_t ws_bytes = 0) {
+                    void* ws = nullptr, size_t ws_bytes = 0, bool compact_ws = false) {
   if (M < 0 || N < 0 || K < 0) return fail(QR_EINVAL, "%s: negative size", who);
   if (M == 0 || N == 0) return QR_OK;
   if (!A || !B || !out) return fail(QR_EINVAL, "%s: null pointer", who);
@@ -1458,15 +1490,19 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   // loop of a tile is split over several CTAs so that all SMs stream weights
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   if (ws && tuning("gemm_splitk", 1) != 0) {
-    size_t need = 0;
-    const int splits = decode_splits(M, N, K, &need);
+    size_t need = 0, compact_counters = 0;
+    int splits = decode_splits(M, N, K, &need, &compact_counters);
+    if (!compact_ws) {   // fixed counter region in front of the partial tiles
+      if (compact_counters > kWsCounterRegion) splits = 1;
+      need = need - compact_counters + kWsCounterRegion;
+    }
     if (splits > 1) {
       if (ws_bytes < need) return fail(QR_EINVAL, "%s: workspace of %zu bytes is too small, %zu needed", who, ws_bytes, need);
       if (((uintptr_t)ws & 255) != 0) return fail(QR_EALIGN, "%s: workspace must be 256-byte aligned", who);
-      const size_t tiles = (size_t)((N + kBM - 1) / kBM) * (size_t)((M + bn - 1) / bn);
       p.splits = splits;
       p.ws_counter = reinterpret_cast<int*>(ws);
-      p.ws_partial = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(ws) + ((tiles * 4 + 255) & ~(size_t)255));
+      p.ws_partial = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(ws) +
+                                                (compact_ws ? compact_counters : kWsCounterRegion));
     }
   }
   p.rowsP = (int)N; p.rowsQ = (int)M;
@@ -1494,11 +1530,19 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
                                     (cudaStream_t)stream);
 }
 
-size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+// scratch of the decode path (split-K) in the compact layout of the built-in array of qr_linear_i4_f16_static
+static size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0 || M > qr::tuning("gemm_swap_max_m", 64)) return 0;
   size_t bytes = 0;
   qr::decode_splits(M, N, K, &bytes);
   return bytes;
+}
+
+size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || M > qr::tuning("gemm_swap_max_m", 64)) return 0;
+  size_t bytes = 0, compact_counters = 0;
+  if (qr::decode_splits(M, N, K, &bytes, &compact_counters) <= 1 || compact_counters > qr::kWsCounterRegion) return 0;
+  return bytes - compact_counters + qr::kWsCounterRegion;
 }
 
 // ---- scratch that lives inside the library image (see qr_linear_i4_f16_static) -----------------
@@ -1527,7 +1571,7 @@ static int static_scratch_ptr(void** out) {
 
 int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
                             int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
-  const size_t need = qr_linear_workspace_bytes(M, N, K);
+  const size_t need = decode_workspace_bytes(M, N, K);
   if (need > qr::kStaticScratchBytes)
     return qr::fail(QR_EUNSUPPORTED,
                     "qr_linear_i4_f16_static: this shape needs %zu bytes of scratch, the built-in scratch holds %zu; "
@@ -1544,7 +1588,7 @@ int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, 
   qr::decode_splits(M, N, K, nullptr, &counter_bytes);
   QR_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, (cudaStream_t)stream));
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_static", A, B, M, N, K, out, ldo, sA, sB, bias,
-                                    (cudaStream_t)stream, scratch, qr::kStaticScratchBytes);
+                                    (cudaStream_t)stream, scratch, qr::kStaticScratchBytes, true);
 }
 
 int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,

