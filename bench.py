@@ -494,13 +494,14 @@ def main():
             "kernel_ms": per, "clocks": clocks}
 
     if not args.no_e2e:
-        e2e_ms, h2d, d2h = e2e_run(qb, layers, M, dev, max(3, min(args.steps, 10)), 3, work)
+        e2e_ms, h2d, d2h = e2e_run(qb, layers, M, dev, max(3, min(args.steps, 10)), 6, work)
         if dist is not None:
             t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             e2e_ms = float(t.item())
         line["e2e"] = {"value": total_ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                       "host_link_gbs": (h2d + d2h) / (e2e_ms * 1e-3) / 1e9,
                        "api": "torch.nn.Sequential(quarot_b200.nn.[Hadamard]Quantizer, quarot_b200.nn.Linear4bit) "
                               "with pinned host activations in and host fp16 results out"}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
