@@ -140,7 +140,8 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
  * arrives last reduces, nobody waits).  qr_linear_workspace_bytes returns the bytes needed for a
  * shape (0 when no split would be used).  The workspace must be 256-byte aligned device memory that
  * was zeroed once before its first use (the kernel leaves the counters at zero) and must not be
- * shared by launches that may overlap on the GPU.  Same result as qr_linear_i4_f16, bit for bit.
+ * shared by launches that may overlap on the GPU.  Its first 64 KiB hold the arrival counters whatever the
+ * shape and the partial tiles follow, so calls of different shapes may share one workspace.  Same result as qr_linear_i4_f16, bit for bit.
  * No upstream counterpart: upstream runs one CUTLASS GEMM without split-K (quarot/kernels/gemm.cu:16-41). */
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
