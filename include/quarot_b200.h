@@ -134,6 +134,20 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
                      const void* bias, int64_t M, int64_t N, int64_t K,
                      void* out, int64_t ldo, void* stream);
 
+/* qr_linear_i4_f16 whose result lands in several matrices at once: outs[0 .. n_outs) (n_outs <= 8) each point
+ * to an [M, N] block with row pitch ldo, in the memory of this GPU or of a peer GPU that this process can
+ * address (peer access enabled, or a mapped symmetric allocation).  The epilogue issues one tiled TMA store per
+ * destination, so in a column split over G GPUs (rank r owns output channels [r N/G, (r+1) N/G) of a linear, every
+ * rank sees all token rows) each rank passes the address of its column block inside every rank's full [M, N_total]
+ * matrix and no all-gather is needed afterwards: the slabs cross NVLink while the tensor cores work on the next
+ * tile.  The caller orders the launches of the ranks around the buffers (a barrier before the matrices are
+ * overwritten and one before they are read).  Needs M > 128, 16-byte aligned outputs and ldo % 8 == 0
+ * (QR_EUNSUPPORTED / QR_EALIGN otherwise).  No upstream counterpart: upstream has no multi-GPU code on this path
+ * (quarot/nn/linear.py:42-56 runs on one device). */
+int qr_linear_i4_f16_outs(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
+                          const void* bias, int64_t M, int64_t N, int64_t K,
+                          void* const* outs, int n_outs, int64_t ldo, void* stream);
+
 /* Decode-sized M (M <= 64) is bound by streaming the weights; with few output tiles a single pass
  * leaves most SMs idle, so the K loop of every tile can be split over several CTAs that meet in a
  * caller-provided scratch buffer (int32 partial tiles + one arrival counter per tile; the split that

@@ -207,3 +207,25 @@ def linear_i4(q_x, scales_x, weight, weight_scales, bias=None, out=None, use_wor
                                          out.data_ptr(), ldo, _stream(dev))
         _lib.check(rc, "linear_i4")
     return out.view(*A_shape_excl_last, N) if out.is_contiguous() else out
+
+
+def linear_i4_outs(q_x, scales_x, weight, weight_scales, bias, out_ptrs, ldo):
+    """Fused Linear4bit forward whose [M, N] result is written to several places at once: `out_ptrs` are device
+    addresses (ints) of [M, N] blocks with row pitch `ldo`, on this GPU or on peers this process can address.
+    One tiled store per destination leaves the epilogue; see qr_linear_i4_f16_outs.  Returns nothing."""
+    assert q_x.shape[-1] % 32 == 0, "A.shape[-1]: {} must be multiplication of 32".format(q_x.shape[-1])
+    A, _ = flatten_last_dim_and_return_shape(q_x)
+    sx = scales_x.view(-1)
+    sw = weight_scales.view(-1)
+    dev = _check_cuda_contig("linear_i4_outs", q_x=A, scales_x=sx, weight=weight, weight_scales=sw, bias=bias)
+    M, N, K = A.shape[0], weight.shape[0], A.shape[1] * 2
+    if weight.shape[1] != A.shape[1] or sx.shape[0] != M or sw.shape[0] != N:
+        raise RuntimeError("linear_i4_outs: operand sizes do not match")
+    import ctypes
+    arr = (ctypes.c_void_p * len(out_ptrs))(*[int(p) for p in out_ptrs])
+    with torch.cuda.device(dev):
+        rc = _lib_c.qr_linear_i4_f16_outs(A.data_ptr(), sx.data_ptr(), weight.data_ptr(), sw.data_ptr(),
+                                          bias.data_ptr() if bias is not None else None, M, N, K,
+                                          arr, len(out_ptrs), int(ldo), _stream(dev))
+        _lib.check(rc, "linear_i4_outs")
+

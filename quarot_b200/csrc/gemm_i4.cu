@@ -60,6 +60,7 @@ struct GemmParams {
   long long* trace;      // optional device buffer [2 CTAs][8 slots][64] for clock64 stamps of cluster 0, or null
   int debug;             // timing experiments only (results are wrong when non-zero)
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
+  int n_outs;            // 2-CTA kernel: number of output matrices that receive the result (1, or one per GPU of a column split)
   int tma_out;           // 2-CTA kernel: the output has a tensor map (16-byte aligned base and row pitch): tiled stores
   int* status;
 };
@@ -403,6 +404,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 // TMA loads are CTA-local (no multicast of data); the MMA-completion signal is one commit
 // delivered to the same barrier in both CTAs.
 constexpr int kBN2 = 256;            // N of the pair tile; each CTA holds kBN2 / 2 rows of operand Q
+constexpr int kMaxOuts = 8;          // output matrices one launch can write (the GPUs of a column split)
+struct OutMaps { CUtensorMap m[kMaxOuts]; };
 constexpr int kRows2 = kBM + kBN2 / 2;  // operand rows per CTA per stage (128 P + 128 Q)
 
 template <int PST, int IST>
@@ -445,7 +448,7 @@ __device__ __forceinline__ int widen_index2(int w) {
 template <int PST, int IST, int MODE>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                   const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
+                   const __grid_constant__ OutMaps tmOs, const GemmParams p) {
   using L = SmemLayout2<PST, IST>;
   constexpr int ACC = 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -475,7 +478,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   if (threadIdx.x == 32) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmO) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmOs.m[0]) : "memory");
   }
 
   if (threadIdx.x == 0) {
@@ -718,7 +721,9 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && row0 < p.rowsP && tq * kBN2 + c0 < p.rowsQ) {
-            tma_store_2d(&tmO, stg_u32, tq * kBN2 + c0, row0);
+            // one tiled store per destination: the block goes to this GPU's output and, in a column split, straight
+            // into the peers' copies of the full matrix over NVLink
+            for (int g = 0; g < p.n_outs; ++g) tma_store_2d(&tmOs.m[g], stg_u32, tq * kBN2 + c0, row0);
             bulk_commit_group();
           }
         }
@@ -1351,7 +1356,7 @@ static int launch_gemm_2sm_ts(const CUtensorMap& tmP, const CUtensorMap& tmQ, co
 }
 
 template <int PST, int IST, int MODE>
-static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const CUtensorMap& tmO, const GemmParams& p,
+static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const OutMaps& tmO, const GemmParams& p,
                            int grid_cap, cudaStream_t st) {
   using L = SmemLayout2<PST, IST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
@@ -1421,7 +1426,8 @@ constexpr size_t kWsCounterRegion = 64u << 10;
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
-                    void* ws = nullptr, size_t ws_bytes = 0, bool compact_ws = false) {
+                    void* ws = nullptr, size_t ws_bytes = 0, bool compact_ws = false,
+                    void* const* more_outs = nullptr, int n_more = 0) {
   if (M < 0 || N < 0 || K < 0) return fail(QR_EINVAL, "%s: negative size", who);
   if (M == 0 || N == 0) return QR_OK;
   if (!A || !B || !out) return fail(QR_EINVAL, "%s: null pointer", who);
@@ -1443,7 +1449,9 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   p.debug = tuning("gemm_debug", 0);
   p.trace = reinterpret_cast<long long*>(debug_trace_ptr());
   p.bias = reinterpret_cast<const __half*>(bias);
-  p.tma_out = 0;
+  p.tma_out = 0; p.n_outs = 1;
+  if (n_more > 0 && (swap || M <= kBM || tuning("gemm_2sm", 1) == 0 || tuning("gemm_ts", 0) != 0))
+    return fail(QR_EUNSUPPORTED, "%s: several outputs are served by the prefill kernel only (more than %d rows)", who, kBM);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
   CUtensorMap tmP, tmQ;
@@ -1461,13 +1469,21 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
       return launch_gemm_2sm_ts<2, MODE>(tmP, tmQ, p, grid_cap, st);
     }
     // tiled stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element-wise
-    CUtensorMap tmO;
+    OutMaps tmO;
     p.tma_out = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) && tuning("gemm_tma_out", 1) != 0;
+    p.n_outs = 1;
     if (p.tma_out) {
-      if ((rc = make_out_map(&tmO, out, M, N, ldo, MODE == MODE_I32))) return rc;
+      if ((rc = make_out_map(&tmO.m[0], out, M, N, ldo, MODE == MODE_I32))) return rc;
+      for (int g = 0; g < n_more; ++g) {
+        if (!aligned16(more_outs[g])) return fail(QR_EALIGN, "%s: every output must be 16-byte aligned", who);
+        if ((rc = make_out_map(&tmO.m[1 + g], more_outs[g], M, N, ldo, MODE == MODE_I32))) return rc;
+      }
+      p.n_outs = 1 + n_more;
     } else {
-      tmO = tmP;   // never dereferenced
+      if (n_more > 0) return fail(QR_EALIGN, "%s: several outputs need a 16-byte aligned base and row pitch", who);
+      tmO.m[0] = tmP;   // never dereferenced
     }
+    for (int g = p.n_outs; g < kMaxOuts; ++g) tmO.m[g] = tmO.m[0];
     return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, tmO, p, grid_cap, st);
   }
   if (!swap) {
@@ -1528,6 +1544,16 @@ int qr_linear_i4_f16(const uint8_t* A, const void* sA, const uint8_t* B, const v
                      int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16", A, B, M, N, K, out, ldo, sA, sB, bias,
                                     (cudaStream_t)stream);
+}
+
+int qr_linear_i4_f16_outs(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
+                          int64_t M, int64_t N, int64_t K, void* const* outs, int n_outs, int64_t ldo, void* stream) {
+  if (!outs || n_outs < 1 || n_outs > qr::kMaxOuts)
+    return qr::fail(QR_EINVAL, "qr_linear_i4_f16_outs: between 1 and %d outputs", qr::kMaxOuts);
+  for (int g = 0; g < n_outs; ++g)
+    if (!outs[g]) return qr::fail(QR_EINVAL, "qr_linear_i4_f16_outs: null output %d", g);
+  return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_outs", A, B, M, N, K, outs[0], ldo, sA, sB, bias,
+                                    (cudaStream_t)stream, nullptr, 0, false, outs + 1, n_outs - 1);
 }
 
 // scratch of the decode path (split-K) in the compact layout of the built-in array of qr_linear_i4_f16_static

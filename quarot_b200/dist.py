@@ -100,3 +100,44 @@ class ColumnSplitLinear4bit(torch.nn.Module):
                                                                         device=local2.device)
         out.view(m, self.world, n_loc).copy_(slabs.permute(1, 0, 2))
         return out.view(*lead, self.out_features)
+
+
+class SymmetricOutput:
+    """An fp16 [rows, cols] matrix that exists at the same place in a symmetric allocation on every rank of the
+    group, together with the device addresses under which THIS process can write every rank's copy over NVLink
+    (torch.distributed symmetric memory).  `barrier()` is a device-side barrier over the ranks on the current
+    stream: one before the copies are overwritten, one before they are read."""
+
+    def __init__(self, rows, cols, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only, no multicast objects
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.local = symm_mem.empty((rows, cols), dtype=torch.float16, device=device)
+        self.handle = symm_mem.rendezvous(self.local, self.group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.rows, self.cols = rows, cols
+
+    def barrier(self):
+        self.handle.barrier()
+
+
+class FusedColumnSplitLinear4bit(ColumnSplitLinear4bit):
+    """Column split without the all-gather: the epilogue of the local GEMM stores every tile of its [M, N/G] slab
+    straight into the column block [r N/G, (r+1) N/G) of EVERY rank's full [M, N] matrix (one tiled store per
+    rank, the remote ones cross NVLink while the tensor cores work on the next tile)."""
+
+    def forward(self, x, target):
+        """x: PackedQuantizedTensor with all token rows; target: SymmetricOutput of shape [M, N].  Returns the
+        local [M, N] matrix after all ranks' slabs have landed."""
+        assert type(x) == _ops.PackedQuantizedTensor
+        n_loc = self.weight.shape[0]
+        if target.cols != self.out_features or n_loc * self.world != self.out_features:
+            raise RuntimeError("FusedColumnSplitLinear4bit: target has %d columns, expected %d" % (target.cols, self.out_features))
+        col_bytes = 2 * n_loc * self.rank
+        target.barrier()          # nobody still reads the previous contents
+        _ops.linear_i4_outs(x.quantized_x, x.scales_x, self.weight, self.weight_scales, self.bias,
+                            [p + col_bytes for p in target.ptrs], target.cols)
+        target.barrier()          # every rank's slab is in every copy
+        return target.local
+

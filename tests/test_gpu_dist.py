@@ -1,5 +1,6 @@
 """Two-GPU equivalence tests (NCCL): run only where at least two GPUs are visible.
-Row sharding and the column split must reproduce the single-GPU result bit for bit."""
+Row sharding and the column split (with the all-gather, and with the epilogue writing into the peers' matrices)
+must reproduce the single-GPU result bit for bit."""
 import os
 import socket
 
@@ -21,6 +22,7 @@ def _worker(rank, world, port, ret):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
+    os.environ["TORCH_SYMM_MEM_DISABLE_MULTICAST"] = "1"      # plain peer stores only, no multicast objects
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -42,7 +44,15 @@ def _worker(rank, world, port, ret):
         # output channels split, all-gather of the fp16 slabs
         col = qd.ColumnSplitLinear4bit(w, sw, None)
         cols_ok = torch.equal(col(quant(x)), full)
-        ret[rank] = (bool(rows_ok), bool(cols_ok))
+        # the same split with the epilogue storing straight into every rank's matrix (no all-gather)
+        fused = qd.FusedColumnSplitLinear4bit(w, sw, None)
+        target = qd.SymmetricOutput(M, N, dev)
+        fused_ok = True
+        for _ in range(3):
+            got = fused(quant(x), target)
+            torch.cuda.synchronize()
+            fused_ok = fused_ok and bool(torch.equal(got, full))
+        ret[rank] = (bool(rows_ok), bool(cols_ok), bool(fused_ok))
     finally:
         dist.destroy_process_group()
 
@@ -53,4 +63,4 @@ def test_two_gpu_sharding_matches_single_gpu():
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
-    assert dict(ret) == {0: (True, True), 1: (True, True)}
+    assert dict(ret) == {0: (True, True, True), 1: (True, True, True)}

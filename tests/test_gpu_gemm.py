@@ -261,3 +261,25 @@ def test_one_workspace_serves_calls_of_different_shapes():
         a, sx, w, sw, want = cases[shape]
         assert torch.equal(qb.linear_i4(a, sx, w, sw), want), shape
     assert _lib.kernel_status() == 0
+
+
+def test_linear_into_several_outputs_at_once():
+    """qr_linear_i4_f16_outs: the epilogue stores every block to each destination (here three column blocks of
+    local matrices standing in for the ranks of a column split); bits equal the single-output call."""
+    M, N, K = 520, 1000, 1024
+    a, w = _rand_packed(M, K, 31).to(DEV), _rand_packed(N, K, 32).to(DEV)
+    sx = (torch.rand(M) * 0.5 + 0.05).half().to(DEV)
+    sw = (torch.rand(N) * 0.015 + 0.005).half().to(DEV)
+    bias = torch.randn(N).half().to(DEV)
+    want = qb.linear_i4(a, sx, w, sw, bias)
+    pitch, off = 3 * N + 8, N + 8          # column block [off, off + N) of three wider matrices
+    bufs = [torch.full((M, pitch), 3.0, dtype=torch.float16, device=DEV) for _ in range(3)]
+    qb.linear_i4_outs(a, sx, w, sw, bias, [b.data_ptr() + 2 * off for b in bufs], pitch)
+    torch.cuda.synchronize()
+    for b in bufs:
+        assert torch.equal(b[:, off:off + N], want)
+        assert bool((b[:, :off] == 3.0).all()) and bool((b[:, off + N:] == 3.0).all())
+    with pytest.raises(RuntimeError):      # decode-sized calls are not served by this entry point
+        qb.linear_i4_outs(a[:8], sx[:8], w, sw, bias, [bufs[0].data_ptr(), bufs[1].data_ptr()], pitch)
+    assert _lib.kernel_status() == 0
+
