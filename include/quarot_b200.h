@@ -148,6 +148,21 @@ int qr_linear_i4_f16_outs(const uint8_t* A, const void* sA, const uint8_t* B, co
                           const void* bias, int64_t M, int64_t N, int64_t K,
                           void* const* outs, int n_outs, int64_t ldo, void* stream);
 
+/* Gate and up projection of a LLaMA MLP as one GEMM with the SwiGLU product applied in the epilogue:
+ *   out[m, c] = fp16( fp16(silu(g)) * u ),  g = fp16(acc_gate[m,c] * (sA[m] * s_gate[c])),  u likewise,
+ * silu(g) = g / (1 + exp(-g)) evaluated in fp32 -- the fp16 arithmetic of
+ * act_fn(gate_proj(x)) * up_proj(x) in the MLP that upstream subclasses
+ * (e2e/quantized_llama/modeling_llama.py:105-119 with Linear4bit.forward, quarot/nn/linear.py:42-56).
+ *   B  [N2, K/2], sB [N2]: gate and up weights (and scales) interleaved in groups of 128 output channels:
+ *       rows [256 t, 256 t + 128) = gate channels [128 t, 128 t + 128), rows [256 t + 128, 256 t + 256) = the
+ *       same up channels; N2 = 2 x intermediate size, a multiple of 256;
+ *   out [M, N2/2] fp16 with row pitch ldo (ldo % 8 == 0, 16-byte aligned).
+ * Neither projection is written to memory.  Needs M > 128 (QR_EUNSUPPORTED otherwise: run qr_linear_i4_f16 on
+ * the interleaved weights and apply the product separately).  No upstream counterpart: upstream launches the two
+ * Linear4bit modules and two elementwise kernels. */
+int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
+                            int64_t M, int64_t N2, int64_t K, void* out, int64_t ldo, void* stream);
+
 /* Decode-sized M (M <= 64) is bound by streaming the weights; with few output tiles a single pass
  * leaves most SMs idle, so the K loop of every tile can be split over several CTAs that meet in a
  * caller-provided scratch buffer (int32 partial tiles + one arrival counter per tile; the split that

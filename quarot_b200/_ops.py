@@ -229,3 +229,36 @@ def linear_i4_outs(q_x, scales_x, weight, weight_scales, bias, out_ptrs, ldo):
                                           arr, len(out_ptrs), int(ldo), _stream(dev))
         _lib.check(rc, "linear_i4_outs")
 
+
+def linear_i4_swiglu(q_x, scales_x, weight_gu, scales_gu, out=None):
+    """silu(gate_proj(x)) * up_proj(x) as one GEMM with the product in the epilogue.
+
+    weight_gu uint8 [2 I, K/2] and scales_gu fp16 [2 I] hold the gate and up weights interleaved in groups of 128
+    output channels (see `interleave_gate_up`).  Returns fp16 [..., I].  Needs more than 128 token rows."""
+    assert q_x.shape[-1] % 32 == 0, "A.shape[-1]: {} must be multiplication of 32".format(q_x.shape[-1])
+    A, A_shape_excl_last = flatten_last_dim_and_return_shape(q_x)
+    sx = scales_x.view(-1)
+    sw = scales_gu.view(-1)
+    dev = _check_cuda_contig("linear_i4_swiglu", q_x=A, scales_x=sx, weight=weight_gu, weight_scales=sw)
+    M, N2, K = A.shape[0], weight_gu.shape[0], A.shape[1] * 2
+    if weight_gu.shape[1] != A.shape[1] or sx.shape[0] != M or sw.shape[0] != N2:
+        raise RuntimeError("linear_i4_swiglu: operand sizes do not match")
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((M, N2 // 2), dtype=torch.float16, device=dev)
+        rc = _lib_c.qr_linear_i4_swiglu_f16(A.data_ptr(), sx.data_ptr(), weight_gu.data_ptr(), sw.data_ptr(),
+                                            M, N2, K, out.data_ptr(), out.stride(0), _stream(dev))
+        _lib.check(rc, "linear_i4_swiglu")
+    return out.view(*A_shape_excl_last, N2 // 2) if out.is_contiguous() else out
+
+
+def interleave_gate_up(gate, up, group=128):
+    """Rows of `gate` and `up` ([I, ...], same shape) interleaved in groups of `group` rows:
+    [gate[0:g]; up[0:g]; gate[g:2g]; up[g:2g]; ...] -- the operand layout of linear_i4_swiglu."""
+    if gate.shape != up.shape or gate.shape[0] % group:
+        raise ValueError("interleave_gate_up: shapes %s / %s, rows must be a multiple of %d" % (tuple(gate.shape), tuple(up.shape), group))
+    t = gate.shape[0] // group
+    rest = tuple(gate.shape[1:])
+    both = torch.stack((gate.reshape(t, group, *rest), up.reshape(t, group, *rest)), dim=1)
+    return both.reshape(2 * gate.shape[0], *rest).contiguous()
+

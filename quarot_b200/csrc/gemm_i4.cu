@@ -60,6 +60,7 @@ struct GemmParams {
   long long* trace;      // optional device buffer [2 CTAs][8 slots][64] for clock64 stamps of cluster 0, or null
   int debug;             // timing experiments only (results are wrong when non-zero)
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
+  int swiglu;            // 2-CTA kernel, fp16 mode: columns [0,128) / [128,256) of a tile are gate / up channels; out = silu(gate) * up
   int n_outs;            // 2-CTA kernel: number of output matrices that receive the result (1, or one per GPU of a column split)
   int tma_out;           // 2-CTA kernel: the output has a tensor map (16-byte aligned base and row pitch): tiled stores
   int* status;
@@ -667,7 +668,57 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
         if (q4 == 0) stamp(lane, 9 + 2 * tl, 7);
       };
-      if (p.tma_out) {
+      if (MODE == MODE_F16 && p.swiglu) {
+        // Gate and up projections computed as ONE GEMM over row-interleaved weights: columns [0,128) of the tile are
+        // 128 gate channels, columns [128,256) the same 128 up channels.  The epilogue applies the fp16 arithmetic
+        // of  act_fn(gate_proj(x)) * up_proj(x)  (both products rounded to fp16, SiLU evaluated in fp32 and rounded,
+        // product rounded) and stores 128 columns of the [M, N/2] result: neither projection is ever written out.
+        const int row0 = tp * 2 * kBM + (int)rank * kBM + q4 * 32;
+#pragma unroll 1
+        for (int c0 = 0; c0 < kBN2 / 2; c0 += 64) {
+#pragma unroll 1
+          for (int q16 = 0; q16 < 4; ++q16) {
+            uint32_t rg[32], ru[32];
+            const uint32_t tcol = (uint32_t)(a * kBN2 + c0 + 16 * q16);
+            tmem_ld16(tmem_base + ((uint32_t)(q4 * 32) << 16) + tcol, rg);
+            tmem_ld16(tmem_base + ((uint32_t)(q4 * 32) << 16) + tcol + kBN2 / 2, ru);
+            if (c0 + 64 >= kBN2 / 2 && q16 == 3) release_acc();
+            uint4 pk[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              __half2* hh = reinterpret_cast<__half2*>(&pk[e]);
+#pragma unroll
+              for (int j2 = 0; j2 < 4; ++j2) {
+                float hv[2];
+#pragma unroll
+                for (int t = 0; t < 2; ++t) {
+                  const int j = 8 * e + 2 * j2 + t;
+                  const int jc = c0 + 16 * q16 + j;
+                  const __half g = __float2half_rn((float)(int32_t)rg[j] * (sp * sqf[jc]));
+                  const __half u = __float2half_rn((float)(int32_t)ru[j] * (sp * sqf[kBN2 / 2 + jc]));
+                  const float gf = __half2float(g);
+                  const __half act = __float2half_rn(__fdiv_rn(gf, 1.0f + expf(-gf)));
+                  hv[t] = __half2float(act) * __half2float(u);
+                }
+                hh[j2] = __floats2half2_rn(hv[0], hv[1]);
+              }
+            }
+            if (q16 == 0) {
+              if (lane == 0) bulk_wait_read_all();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int e = 0; e < 2; ++e)
+              *reinterpret_cast<uint4*>(stg + lane * 128 + ((((uint32_t)(2 * q16 + e)) ^ my_sw) << 4)) = pk[e];
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.rowsP) {
+            for (int g = 0; g < p.n_outs; ++g) tma_store_2d(&tmOs.m[g], stg_u32, tq * (kBN2 / 2) + c0, row0);
+            bulk_commit_group();
+          }
+        }
+      } else if (p.tma_out) {
         const int row0 = tp * 2 * kBM + (int)rank * kBM + q4 * 32;
 #pragma unroll 1
         for (int c0 = 0; c0 < kBN2; c0 += CW) {
@@ -1427,7 +1478,7 @@ template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
                     void* ws = nullptr, size_t ws_bytes = 0, bool compact_ws = false,
-                    void* const* more_outs = nullptr, int n_more = 0) {
+                    void* const* more_outs = nullptr, int n_more = 0, bool swiglu = false) {
   if (M < 0 || N < 0 || K < 0) return fail(QR_EINVAL, "%s: negative size", who);
   if (M == 0 || N == 0) return QR_OK;
   if (!A || !B || !out) return fail(QR_EINVAL, "%s: null pointer", who);
@@ -1436,7 +1487,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   if (K > 131071) return fail(QR_EUNSUPPORTED, "%s: K = %lld exceeds the int32 headroom of the x256 accumulator", who, (long long)K);
   if (M > (1 << 30) || N > (1 << 30)) return fail(QR_EUNSUPPORTED, "%s: dimension too large", who);
   if (!aligned16(A) || !aligned16(B)) return fail(QR_EALIGN, "%s: operands must be 16-byte aligned", who);
-  if (ldo < N) return fail(QR_EINVAL, "%s: ldo < N", who);
+  if (!swiglu && ldo < N) return fail(QR_EINVAL, "%s: ldo < N", who);
   int* status = kernel_status_ptr();
   if (!status) return fail(QR_ENOTREADY, "%s: no CUDA device", who);
 
@@ -1449,7 +1500,15 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   p.debug = tuning("gemm_debug", 0);
   p.trace = reinterpret_cast<long long*>(debug_trace_ptr());
   p.bias = reinterpret_cast<const __half*>(bias);
-  p.tma_out = 0; p.n_outs = 1;
+  p.tma_out = 0; p.n_outs = 1; p.swiglu = 0;
+  if (swiglu) {
+    if (swap || M <= kBM || tuning("gemm_2sm", 1) == 0 || tuning("gemm_ts", 0) != 0)
+      return fail(QR_EUNSUPPORTED, "%s: served by the prefill kernel only (more than %d rows)", who, kBM);
+    if (N % kBN2 != 0) return fail(QR_EINVAL, "%s: N = %lld must be a multiple of %d (interleaved gate/up rows)", who, (long long)N, kBN2);
+    if (bias) return fail(QR_EUNSUPPORTED, "%s: bias is not supported", who);
+    if (!aligned16(out) || ldo % 8 != 0) return fail(QR_EALIGN, "%s: output must be 16-byte aligned with ldo %% 8 == 0", who);
+    if (ldo < N / 2) return fail(QR_EINVAL, "%s: ldo < N / 2", who);
+  }
   if (n_more > 0 && (swap || M <= kBM || tuning("gemm_2sm", 1) == 0 || tuning("gemm_ts", 0) != 0))
     return fail(QR_EUNSUPPORTED, "%s: several outputs are served by the prefill kernel only (more than %d rows)", who, kBM);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
@@ -1472,7 +1531,10 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
     OutMaps tmO;
     p.tma_out = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) && tuning("gemm_tma_out", 1) != 0;
     p.n_outs = 1;
-    if (p.tma_out) {
+    if (swiglu) {
+      p.swiglu = 1; p.tma_out = 1;
+      if ((rc = make_out_map(&tmO.m[0], out, M, N / 2, ldo, false))) return rc;
+    } else if (p.tma_out) {
       if ((rc = make_out_map(&tmO.m[0], out, M, N, ldo, MODE == MODE_I32))) return rc;
       for (int g = 0; g < n_more; ++g) {
         if (!aligned16(more_outs[g])) return fail(QR_EALIGN, "%s: every output must be 16-byte aligned", who);
@@ -1554,6 +1616,12 @@ int qr_linear_i4_f16_outs(const uint8_t* A, const void* sA, const uint8_t* B, co
     if (!outs[g]) return qr::fail(QR_EINVAL, "qr_linear_i4_f16_outs: null output %d", g);
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_outs", A, B, M, N, K, outs[0], ldo, sA, sB, bias,
                                     (cudaStream_t)stream, nullptr, 0, false, outs + 1, n_outs - 1);
+}
+
+int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
+                            int64_t M, int64_t N2, int64_t K, void* out, int64_t ldo, void* stream) {
+  return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_swiglu_f16", A, B, M, N2, K, out, ldo, sA, sB, nullptr,
+                                    (cudaStream_t)stream, nullptr, 0, false, nullptr, 0, true);
 }
 
 // scratch of the decode path (split-K) in the compact layout of the built-in array of qr_linear_i4_f16_static

@@ -45,3 +45,32 @@ def fuse_modules(model):
                     mod[i + 1] = torch.nn.Identity()
                     count += 1
     return count
+
+
+class SwiGLULinear4bit(torch.nn.Module):
+    """gate_proj and up_proj of a LLaMA MLP (two Linear4bit modules without bias) as one module that returns
+    act_fn(gate_proj(x)) * up_proj(x) for a PackedQuantizedTensor x: one GEMM over the row-interleaved weights with
+    the SiLU product in its epilogue, so neither projection is written to memory.  The interleaved copy is built
+    once here from the modules' canonical [N, K/2] buffers (the checkpoint layout is not changed)."""
+
+    def __init__(self, gate_proj, up_proj):
+        super().__init__()
+        if gate_proj.bias is not None or up_proj.bias is not None:
+            raise ValueError("SwiGLULinear4bit: projections with bias are not supported")
+        self.intermediate_size = gate_proj.weight.shape[0]
+        self.register_buffer("weight_gu", _ops.interleave_gate_up(gate_proj.weight, up_proj.weight))
+        self.register_buffer("scales_gu", _ops.interleave_gate_up(gate_proj.weight_scales.view(-1),
+                                                                 up_proj.weight_scales.view(-1)))
+
+    def forward(self, x):
+        assert type(x) == _ops.PackedQuantizedTensor
+        rows = x.quantized_x.numel() // x.quantized_x.shape[-1]
+        if rows > 128:
+            return _ops.linear_i4_swiglu(x.quantized_x, x.scales_x, self.weight_gu, self.scales_gu)
+        # few token rows: one GEMM over the interleaved weights, the product as separate elementwise kernels
+        both = _ops.linear_i4(x.quantized_x, x.scales_x, self.weight_gu, self.scales_gu)
+        both = both.view(*both.shape[:-1], -1, 2, 128)
+        gate, up = both[..., 0, :], both[..., 1, :]
+        out = torch.nn.functional.silu(gate) * up
+        return out.reshape(*out.shape[:-2], self.intermediate_size)
+

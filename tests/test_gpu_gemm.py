@@ -283,3 +283,46 @@ def test_linear_into_several_outputs_at_once():
         qb.linear_i4_outs(a[:8], sx[:8], w, sw, bias, [bufs[0].data_ptr(), bufs[1].data_ptr()], pitch)
     assert _lib.kernel_status() == 0
 
+
+@pytest.mark.parametrize("M,I,K", [(300, 256, 512), (2048, 1024, 4096), (129, 11008, 256)])
+def test_gate_up_gemm_with_swiglu_epilogue(M, I, K):
+    """silu(gate_proj(x)) * up_proj(x) from one GEMM over interleaved weights: equal to the two Linear4bit calls
+    followed by the fp16 elementwise product (bit for bit against torch's CUDA kernels, and against the CPU
+    oracle up to the last fp16 bit of the exponential)."""
+    a = _rand_packed(M, K, 41)
+    wg, wu = _rand_packed(I, K, 42), _rand_packed(I, K, 43)
+    sx = (torch.rand(M) * 0.05 + 0.005).half()
+    sg = (torch.rand(I) * 0.015 + 0.005).half()
+    su = (torch.rand(I) * 0.015 + 0.005).half()
+    ad, sxd = a.to(DEV), sx.to(DEV)
+    g = qb.linear_i4(ad, sxd, wg.to(DEV), sg.to(DEV))
+    u = qb.linear_i4(ad, sxd, wu.to(DEV), su.to(DEV))
+    w_gu = qb.interleave_gate_up(wg.to(DEV), wu.to(DEV))
+    s_gu = qb.interleave_gate_up(sg.to(DEV), su.to(DEV))
+    got = qb.linear_i4_swiglu(ad, sxd, w_gu, s_gu)
+    unfused = torch.nn.functional.silu(g) * u
+    assert got.shape == (M, I)
+    assert torch.equal(got, unfused)
+    want = O.swiglu_fp16(g.cpu(), u.cpu())
+    diff = (got.cpu().float() - want.float()).abs()
+    assert bool((diff <= want.float().abs() * 2.0 ** -9 + 1e-7).all())
+    assert float((got.cpu() == want).float().mean()) > 0.999
+    assert _lib.kernel_status() == 0
+
+
+def test_swiglu_module_and_small_batches():
+    from quarot_b200.nn.fused import SwiGLULinear4bit
+    I, K = 512, 1024
+    gate, up = qb.nn.Linear4bit(K, I).to(DEV), qb.nn.Linear4bit(K, I).to(DEV)
+    for lin, seed in ((gate, 51), (up, 52)):
+        lin.weight = _rand_packed(I, K, seed).to(DEV)
+        lin.weight_scales = (torch.rand(I, 1) * 0.015 + 0.005).half().to(DEV)
+    fused = SwiGLULinear4bit(gate, up)
+    quant = qb.nn.Quantizer()
+    for rows in (7, 128, 400):
+        x = synth.activations(rows, K, seed=rows).to(DEV)
+        xq = quant(x)
+        want = torch.nn.functional.silu(gate(xq)) * up(xq)
+        assert torch.equal(fused(xq), want), rows
+    assert _lib.kernel_status() == 0
+
