@@ -42,6 +42,10 @@ WORKLOADS = {
     # BASELINE config 4: the two 70B MLP linears with their output channels split over the ranks and an
     # all-gather of the fp16 result; every rank sees all token rows (use --tokens to sweep M)
     "llama2_70b_mlp_colsplit": ("LLAMA2_70B_MLP", 4096),
+    # the MLP block around the path (first of the rows that come after it): quantise -> gate/up -> SiLU product ->
+    # Hadamard + quantise -> down, with the product as separate elementwise kernels or inside the GEMM epilogue
+    "llama2_7b_mlp_swiglu": ("LLAMA2_7B_MLP", 2048),
+    "llama2_70b_mlp_swiglu": ("LLAMA2_70B_MLP", 4096),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -338,6 +342,49 @@ def colsplit_run(args, layers, M, dev, world, rank, dist):
     return res
 
 
+def mlp_run(args, layers, M, dev):
+    """One MLP block: Quantizer -> gate/up Linear4bit -> act_fn(gate) * up -> OnlineHadamard + Quantizer -> down
+    Linear4bit.  Two variants: the product as torch elementwise kernels on the [M, 2 I] GEMM output, and the
+    product inside the GEMM epilogue (the projections never reach memory).  CUDA events, buffers larger than L2."""
+    import quarot_b200 as qb
+    from quarot_b200 import synth
+    from quarot_b200.functional import hadamard as FH
+    (_, K, N2, _), (_, I, Nd, _) = layers
+    nsets = 3
+    xs = [synth.activations_device(M, K, seed=77 + i, device=dev) for i in range(nsets)]
+    wgu = [synth.weights_device(N2, K, seed=88 + i, device=dev) for i in range(nsets)]     # rows already interleaved
+    wd = [synth.weights_device(Nd, I, seed=99 + i, device=dev) for i in range(nsets)]
+    khad = FH.get_hadK(I)[1]
+    table = FH.device_table(khad, dev) if khad > 1 else None
+    both = torch.empty((M, N2), dtype=torch.float16, device=dev)
+    hbuf = torch.empty((M, I), dtype=torch.float16, device=dev)
+    out = torch.empty((M, Nd), dtype=torch.float16, device=dev)
+
+    def step(i, fused):
+        q, s, _ = qb.hadamard_quant(xs[i], None, 0, 1.0)
+        if fused:
+            h = qb.linear_i4_swiglu(q, s, wgu[i][0], wgu[i][1].view(-1), out=hbuf)
+        else:
+            g_u = qb.linear_i4(q, s, wgu[i][0], wgu[i][1].view(-1), out=both).view(M, -1, 2, 128)
+            h = (torch.nn.functional.silu(g_u[:, :, 0, :]) * g_u[:, :, 1, :]).reshape(M, I)
+        q2, s2, _ = qb.hadamard_quant(h, table, khad, 1.0)
+        qb.linear_i4(q2, s2, wd[i][0], wd[i][1].view(-1), out=out)
+
+    res = {}
+    for label, fused in (("unfused_ms", False), ("fused_ms", True)):
+        for i in range(max(args.warmup, nsets)):
+            step(i % nsets, fused)
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            step(i % nsets, fused)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        res[label] = e0.elapsed_time(e1) / args.steps
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -396,6 +443,23 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload.endswith("_mlp_swiglu"):
+        if world > 1:
+            raise SystemExit("bench.py: the MLP-block workload is a single-GPU measurement")
+        res = mlp_run(args, layers, M, dev)
+        ops = layer_ops(layers, M)
+        ms = res["fused_ms"]
+        line = {"metric": metric, "value": ops / (ms * 1e-3) / 1e12, "unit": "TOPS", "n_gpus": 1, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "int4 codes widened to int8, int32 accumulate, fp16 out", "data": "synthetic",
+                "config": dict(config, block="Quantizer -> gate/up GEMM with SiLU product in the epilogue -> "
+                                             "Hadamard+Quantizer -> down GEMM (eager launches)"),
+                "product_as_separate_kernels": {"ms_per_step": res["unfused_ms"],
+                                                "value": ops / (res["unfused_ms"] * 1e-3) / 1e12, "unit": "TOPS"},
+                "tokens_per_s": M / (ms * 1e-3), "gpu_launches": 4 * args.steps}
+        print(json.dumps(line))
+        return 0
 
     if args.workload == "llama2_70b_mlp_colsplit":
         res = colsplit_run(args, layers, M, dev, world, rank, dist)

@@ -15,6 +15,7 @@ LLAMA2_7B = (("qkv", 4096, 12288, False), ("o_proj", 4096, 4096, False),
 LLAMA2_70B = (("qkv", 8192, 10240, False), ("o_proj", 8192, 8192, False),
               ("gate_up", 8192, 57344, False), ("down", 28672, 8192, True))
 LLAMA2_70B_MLP = (("gate_up", 8192, 57344, False), ("down", 28672, 8192, True))
+LLAMA2_7B_MLP = (("gate_up", 4096, 22016, False), ("down", 11008, 4096, True))
 CONFIG0 = (("cfg0", 4096, 4096, True),)
 
 
