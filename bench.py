@@ -46,6 +46,8 @@ WORKLOADS = {
     # Hadamard + quantise -> down, with the product as separate elementwise kernels or inside the GEMM epilogue
     "llama2_7b_mlp_swiglu": ("LLAMA2_7B_MLP", 2048),
     "llama2_70b_mlp_swiglu": ("LLAMA2_70B_MLP", 4096),
+    # the step in front of the path: RMSNorm + Quantizer of the hidden state (fused kernel vs the two modules)
+    "llama2_7b_rmsnorm_quant": ("LLAMA2_7B", 2048),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -385,6 +387,31 @@ def mlp_run(args, layers, M, dev):
     return res
 
 
+def norm_run(args, M, K, dev):
+    """RMSNorm + Quantizer of an [M, K] hidden state: the fused kernel against the two modules (torch elementwise
+    and reduction kernels for the norm, the quantise-only kernel behind it).  CUDA events, rotating inputs > L2."""
+    import quarot_b200 as qb
+    from quarot_b200 import synth
+    from quarot_b200.nn.fused import RMSNormQuantizer
+    nsets = 12
+    xs = [synth.activations_device(M, K, seed=7 + i, device=dev) for i in range(nsets)]
+    fused = RMSNormQuantizer(K)
+    norm, quant = qb.nn.RMSNorm(K), qb.nn.Quantizer()
+    res = {}
+    for label, fn in (("unfused_ms", lambda x: quant(norm(x))), ("fused_ms", fused)):
+        for i in range(max(args.warmup, 3)):
+            fn(xs[i % nsets])
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(args.steps):
+            fn(xs[i % nsets])
+        e1.record()
+        torch.cuda.synchronize(dev)
+        res[label] = e0.elapsed_time(e1) / args.steps
+    return res
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -443,6 +470,19 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.workload == "llama2_7b_rmsnorm_quant":
+        K = layers[0][1]
+        res = norm_run(args, M, K, dev)
+        nbytes = bytes_quant(M, K)
+        line = {"metric": "rmsnorm_quant_gbs", "value": nbytes / (res["fused_ms"] * 1e-3) / 1e9, "unit": "GB/s",
+                "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["fused_ms"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 in, fp32 norm, int4 out",
+                "data": "synthetic", "config": {"workload": args.workload, "tokens_per_gpu": M, "hidden": K,
+                                                "l2": "inputs rotate over 12 buffers (201 MB)"},
+                "modules_unfused": {"ms_per_step": res["unfused_ms"]}, "gpu_launches": args.steps}
+        print(json.dumps(line))
+        return 0
 
     if args.workload.endswith("_mlp_swiglu"):
         if world > 1:

@@ -102,6 +102,17 @@ int qr_hadamard_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx,
                          const void* had_k, int K, float clip,
                          uint8_t* q, void* scales, void* y_out, void* stream);
 
+/* Weight-less RMS normalisation fused in front of the quantiser: the step directly before the path for the
+ * inputs of the q/k/v and gate/up projections.  Replaces RMSNorm.forward (quarot/nn/normalization.py:15-21)
+ * followed by Quantizer.forward (quarot/nn/quantization.py:9-13):
+ *   y = fp16( float(x) * rsqrt(sum(float(x)^2) / mean_dim + eps) ),  then scales and codes of y as in
+ *   qr_hadamard_quant_i4 with K = 0.  One pass over x instead of the eight elementwise / reduction kernels
+ *   (and their fp32 temporaries) of the unfused modules.
+ *   x [rows, n] fp16 with row stride ldx (ldx % 8 == 0, 16-byte aligned), n % 8 == 0, 64 <= n <= 32768;
+ *   q [rows, n/2], scales [rows] fp16, y_out optional [rows, n] fp16 copy of the normalised rows. */
+int qr_rmsnorm_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx, int64_t mean_dim, float eps, float clip,
+                        uint8_t* q, void* scales, void* y_out, void* stream);
+
 /* Standalone quantise-and-pack with caller-provided per-row scales.
  * Replaces sym_quant_host (quarot/kernels/include/quant.h:6-13,
  * quarot/kernels/quant.cu:48-61) behind quarot.sym_quant (quarot/__init__.py:43-46).

@@ -262,3 +262,21 @@ def interleave_gate_up(gate, up, group=128):
     both = torch.stack((gate.reshape(t, group, *rest), up.reshape(t, group, *rest)), dim=1)
     return both.reshape(2 * gate.shape[0], *rest).contiguous()
 
+
+def rmsnorm_quant(x, mean_dim, eps=1e-5, clip=1.0, return_y=False):
+    """Weight-less RMSNorm followed by the per-token quantiser, in one pass over x.
+
+    x fp16 [..., n].  Returns (q uint8 [..., n/2], scales fp16 [rows], y fp16 [..., n] or None)."""
+    assert x.dtype == torch.float16
+    x2, shape_excl_last = flatten_last_dim_and_return_shape(x)
+    dev = _check_cuda_contig("rmsnorm_quant", x=x2)
+    rows, n = x2.shape
+    with torch.cuda.device(dev):
+        q = torch.empty((rows, n // 2), dtype=torch.uint8, device=dev)
+        s = torch.empty((rows,), dtype=torch.float16, device=dev)
+        y = torch.empty((rows, n), dtype=torch.float16, device=dev) if return_y else None
+        rc = _lib_c.qr_rmsnorm_quant_i4(x2.data_ptr(), rows, n, x2.stride(0), int(mean_dim), float(eps), float(clip),
+                                        q.data_ptr(), s.data_ptr(), y.data_ptr() if return_y else None, _stream(dev))
+        _lib.check(rc, "rmsnorm_quant")
+    return (q.view(*shape_excl_last, n // 2), s, y.view(*shape_excl_last, n) if return_y else None)
+

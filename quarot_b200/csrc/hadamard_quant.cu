@@ -209,6 +209,87 @@ quant_rows_kernel(const HadqParams p) {
   }
 }
 
+// RMS normalisation fused in front of the quantiser (the step directly before the path for the QKV and gate/up
+// inputs): y = fp16(x * rsqrt(mean(x^2) + eps)) in fp32 as the weight-less RMSNorm of the reference computes it,
+// then absmax -> scale -> int4 codes of y.  Same structure as quant_rows_kernel; the row-wide reduction carries the
+// sum of squares next to the absmax, and the absmax of y is taken from the absmax of x (rounding is monotone:
+// max_i fp16(|x_i| r) = fp16(max_i |x_i| r)), so one barrier serves both.
+struct RmsQuantParams {
+  const __half* x;
+  int64_t ldx, rows;
+  int n;
+  float eps, mean_dim, clip;
+  uint8_t* q;
+  __half* scales;
+  __half* y_out;     // optional copy of the normalised row, or null
+};
+
+__global__ void __launch_bounds__(1024)
+rmsnorm_quant_rows_kernel(const RmsQuantParams p) {
+  __shared__ float red_max[2][32];
+  __shared__ float red_ss[2][32];
+  const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
+  const int nchunks = p.n >> 3;
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  int parity = 0;
+  for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.ldx);
+    uint4 cur[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xr + tid + j * T) : zero;
+    float amax = 0.0f, ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __half2* h = reinterpret_cast<const __half2*>(&cur[j]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __half22float2(h[e]);
+        ss = __fmaf_rn(f.x, f.x, ss);
+        ss = __fmaf_rn(f.y, f.y, ss);
+      }
+      amax = fmaxf(amax, absmax8(cur[j]));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+      ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    }
+    if (lane == 0) { red_max[parity][warp] = amax; red_ss[parity][warp] = ss; }
+    __syncthreads();
+    float a = (lane < nwarps) ? red_max[parity][lane] : 0.0f;
+    float t = (lane < nwarps) ? red_ss[parity][lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+      t += __shfl_xor_sync(0xffffffffu, t, o);
+    }
+    const float r = rsqrtf(__fdiv_rn(t, p.mean_dim) + p.eps);
+    const float ymax = __half2float(__float2half_rn(a * r));
+    const float s = scale_from_absmax(ymax, p.clip, tid == 0 ? p.scales + row : nullptr);
+    const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+    const bool noclamp = clamp_free(s, p.clip);
+    uint32_t* qo = reinterpret_cast<uint32_t*>(p.q + row * (int64_t)(p.n >> 1));
+    uint4* yo = p.y_out ? reinterpret_cast<uint4*>(p.y_out + row * (int64_t)p.n) : nullptr;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = tid + j * T;
+      if (c < nchunks) {
+        const __half2* h = reinterpret_cast<const __half2*>(&cur[j]);
+        uint4 y;
+        uint32_t* yw = reinterpret_cast<uint32_t*>(&y);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __half22float2(h[e]);
+          const __half2 yh = __floats2half2_rn(f.x * r, f.y * r);
+          yw[e] = *reinterpret_cast<const uint32_t*>(&yh);
+        }
+        qo[c] = quant8_u4(y, s, rcp, noclamp);
+        if (yo) yo[c] = y;
+      }
+    }
+  }
+}
+
 // KT = number of 16-wide k tiles of the dense factor (0 when K == 1).  One thread per group of
 // 32 consecutive outputs; blockDim.x >= n / 32 (rounded up to whole warps).
 // Largest CTA each instantiation is compiled for (bounds the registers per thread).
@@ -652,6 +733,26 @@ int qr_hadamard_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx, co
   if (ldx < n) return qr::fail(QR_EINVAL, "qr_hadamard_quant_i4: ldx < n");
   return qr::run_hadq("qr_hadamard_quant_i4", x, rows, n, ldx, had_k, K, clip, q, scales, y_out, 1, 2,
                       (cudaStream_t)stream);
+}
+
+int qr_rmsnorm_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx, int64_t mean_dim, float eps, float clip,
+                        uint8_t* q, void* scales, void* y_out, void* stream) {
+  if (rows < 0 || n < 0) return qr::fail(QR_EINVAL, "qr_rmsnorm_quant_i4: negative size");
+  if (rows == 0 || n == 0) return QR_OK;
+  if (!x || !q || !scales) return qr::fail(QR_EINVAL, "qr_rmsnorm_quant_i4: null pointer");
+  if (ldx < n) return qr::fail(QR_EINVAL, "qr_rmsnorm_quant_i4: ldx < n");
+  if (mean_dim <= 0) return qr::fail(QR_EINVAL, "qr_rmsnorm_quant_i4: mean_dim must be positive");
+  if (n % 8 != 0 || n < 64 || n > 32768) return qr::fail(QR_EUNSUPPORTED, "qr_rmsnorm_quant_i4: n = %lld (a multiple of 8 in [64, 32768])", (long long)n);
+  if (!qr::aligned16(x) || ldx % 8 != 0 || !qr::aligned16(q) || (y_out && !qr::aligned16(y_out)))
+    return qr::fail(QR_EALIGN, "qr_rmsnorm_quant_i4: x, q and y_out must be 16-byte aligned, ldx % 8 == 0");
+  qr::RmsQuantParams p;
+  p.x = reinterpret_cast<const __half*>(x); p.ldx = ldx; p.rows = rows; p.n = (int)n;
+  p.eps = eps; p.mean_dim = (float)mean_dim; p.clip = clip;
+  p.q = q; p.scales = reinterpret_cast<__half*>(scales); p.y_out = reinterpret_cast<__half*>(y_out);
+  int threads = (((int)n / 8 + 3) / 4 + 31) / 32 * 32;
+  QR_CUDA(qr::launch_kernel(qr::rmsnorm_quant_rows_kernel, dim3(qr::persistent_grid(rows, threads, 1024)), dim3(threads), 0,
+                            (cudaStream_t)stream, false, p));
+  return QR_OK;
 }
 
 }  // extern "C"

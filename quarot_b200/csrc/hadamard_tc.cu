@@ -170,40 +170,45 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
     const int rows = p.MT * 128, K = p.K;
     const int chunks = rows * p.KA * 8;                       // 16-byte chunks of the A operand
     const bool vec = (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.had_k) & 7) == 0);
-    // four chunks per thread and round: the loads of a round are issued before its stores
-    for (int c_base = t; c_base < chunks; c_base += 4 * nt) {
-      uint4 v[4];
-      uint32_t dst[4];
+    // twelve chunks per thread and round (one round for K <= 172): all loads of a round are issued before its
+    // stores, so the set-up costs one trip to L2 instead of one per chunk
+    constexpr int kU = 12;
+    const int row_shift = 10 + (p.MT - 1);                    // log2(rows * 8)
+    for (int c_base = t; c_base < chunks; c_base += kU * nt) {
+      uint2 lo[kU], hi[kU];
+      uint32_t dst[kU];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kU; ++u) {
         const int c = c_base + u * nt;
-        v[u] = make_uint4(0, 0, 0, 0);
+        lo[u] = make_uint2(0, 0);
+        hi[u] = make_uint2(0, 0);
         dst[u] = 0xFFFFFFFFu;
         if (c < chunks) {
-          const int ka = c / (rows * 8);
-          const int rem = c - ka * rows * 8;
+          const int ka = c >> row_shift;
+          const int rem = c - (ka << row_shift);
           const int r = rem >> 3, ch = rem & 7;
           const int c0 = ka * 64 + ch * 8;                      // first hadK column of this chunk
           dst[u] = (uint32_t)(ka * a_atom_bytes + r * 128 + ((ch ^ (r & 7)) << 4));
           if (r < K && c0 < K) {
             const __half* src = p.had_k + (size_t)r * K + c0;
             if (vec) {      // K % 4 == 0: the chunk starts on an 8-byte boundary and holds 4 or 8 valid columns
-              const uint2 lo = __ldg(reinterpret_cast<const uint2*>(src));
-              uint2 hi = make_uint2(0, 0);
-              if (c0 + 8 <= K) hi = __ldg(reinterpret_cast<const uint2*>(src + 4));
-              v[u] = make_uint4(lo.x, lo.y, hi.x, hi.y);
+              lo[u] = __ldg(reinterpret_cast<const uint2*>(src));
+              if (c0 + 8 <= K) hi[u] = __ldg(reinterpret_cast<const uint2*>(src + 4));
             } else {
               __align__(16) __half tmp[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) tmp[e] = (c0 + e < K) ? src[e] : __float2half(0.0f);
-              v[u] = *reinterpret_cast<const uint4*>(tmp);
+              const uint4 v = *reinterpret_cast<const uint4*>(tmp);
+              lo[u] = make_uint2(v.x, v.y);
+              hi[u] = make_uint2(v.z, v.w);
             }
           }
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (dst[u] != 0xFFFFFFFFu) *reinterpret_cast<uint4*>(smem_gen + dst[u]) = v[u];
+      for (int u = 0; u < kU; ++u)
+        if (dst[u] != 0xFFFFFFFFu)
+          *reinterpret_cast<uint4*>(smem_gen + dst[u]) = make_uint4(lo[u].x, lo[u].y, hi[u].x, hi[u].y);
     }
     const int pad_rows = p.KT16 * 16 - K;
     for (int c = t; c < 2 * kTcNB * pad_rows * 8; c += nt) {

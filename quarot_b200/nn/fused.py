@@ -74,3 +74,17 @@ class SwiGLULinear4bit(torch.nn.Module):
         out = torch.nn.functional.silu(gate) * up
         return out.reshape(*out.shape[:-2], self.intermediate_size)
 
+
+class RMSNormQuantizer(torch.nn.Module):
+    """RMSNorm(mean_dim, eps) followed by Quantizer(input_clip_ratio), fused: what stands in front of the q/k/v and
+    gate/up projections of a rotated LLaMA layer (the residual stream keeps the un-normalised x, so the normalised
+    fp16 tensor is never needed on its own)."""
+
+    def __init__(self, mean_dim, eps=1e-5, input_clip_ratio=1.0):
+        super().__init__()
+        self.mean_dim, self.eps, self.input_clip_ratio = mean_dim, eps, input_clip_ratio
+
+    def forward(self, x):
+        q, s, _ = _ops.rmsnorm_quant(x, self.mean_dim, self.eps, self.input_clip_ratio)
+        return _ops.PackedQuantizedTensor(q, s.view(x.shape[:-1]).unsqueeze(1))
+

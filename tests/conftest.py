@@ -16,4 +16,4 @@ def pytest_configure(config):
 
 @pytest.fixture(scope="session")
 def golden():
-    return {name: np.load(os.path.join(GOLDEN, name + ".npz")) for name in ("hadamard", "quantizer", "matmul")}
+    return {name: np.load(os.path.join(GOLDEN, name + ".npz")) for name in ("hadamard", "quantizer", "matmul", "rmsnorm")}

@@ -3,6 +3,7 @@
 Runs the upstream project's own CPU-capable torch functions
 (quarot/functional/hadamard.py: get_hadK, matmul_hadU, matmul_hadUt;
 quarot/functional/quantization.py: sym_quant, pack_i4, unpack_i4;
+quarot/nn/normalization.py: RMSNorm;
 the scale formula of quarot/nn/quantization.py:10 evaluated inline) on small
 seeded inputs and stores inputs and outputs.  The upstream modules are loaded
 by file path with an empty stand-in for the CUDA-only ``fast_hadamard_transform``
@@ -93,7 +94,17 @@ def main():
         c = Q.unpack_i4(ap) @ Q.unpack_i4(bp).T
         mm[tag + "_a"], mm[tag + "_b"], mm[tag + "_c"] = ap.numpy(), bp.numpy(), c.numpy()
     np.savez_compressed(os.path.join(HERE, "matmul.npz"), **mm)
-    for f in ("hadamard.npz", "quantizer.npz", "matmul.npz"):
+    # ---- weight-less RMSNorm (the module in front of the quantiser of the q/k/v and gate/up inputs)
+    N = load(root, "_up_norm", "quarot/nn/normalization.py")
+    gen2 = torch.Generator().manual_seed(20240407)
+    rn = {}
+    for tag, (rows, n) in {"a": (9, 64), "b": (7, 4096), "c": (3, 11008), "d": (4, 8192)}.items():
+        x = outlier_rows(gen2, rows, n)
+        x[0] = 0
+        rn[tag + "_x"] = x.numpy()
+        rn[tag + "_y"] = N.RMSNorm(n, eps=1e-5)(x).numpy()
+    np.savez_compressed(os.path.join(HERE, "rmsnorm.npz"), **rn)
+    for f in ("hadamard.npz", "quantizer.npz", "matmul.npz", "rmsnorm.npz"):
         print(f, os.path.getsize(os.path.join(HERE, f)))
 
 

@@ -227,3 +227,28 @@ def test_online_hadamard_module_and_fusion_agree():
     y = qb.nn.OnlineHadamard(128).to(DEV)(a)
     ok, worst = _had_close(y.cpu(), O.hadamard(a.cpu().float()))
     assert ok, worst
+
+
+@pytest.mark.parametrize("n,rows", [(4096, 33), (8192, 5), (11008, 3), (64, 9), (5120, 4)])
+@pytest.mark.parametrize("clip", [1.0, 0.9])
+def test_rmsnorm_quant_fused(n, rows, clip):
+    """RMSNorm + Quantizer in one pass: the normalised row within fp16 rounding of the fp32 operator (the order of
+    the sum of squares and the rsqrt differ in the last bits), scales and codes bit-exact given that row."""
+    x = synth.activations(rows, n, seed=3 * n + rows)
+    x[0] = 0                                    # zero row: rsqrt(eps) * 0 = 0, scale 0, zero codes
+    q, s, y = qb.rmsnorm_quant(x.to(DEV), n, 1e-5, clip, return_y=True)
+    q, s, y = q.cpu(), s.cpu(), y.cpu()
+    ref = O.rmsnorm_fp16(x, n, 1e-5)
+    err = (y.double() - ref.double()).abs()
+    assert bool((err <= ref.double().abs() * 2.0 ** -10 + 1e-7).all())
+    assert float((y == ref).float().mean()) > 0.99
+    s_ref = O.quantizer_scales(y, clip)
+    assert torch.equal(_bits(s), _bits(s_ref))
+    assert torch.equal(q, O.pack_i4(O.sym_quant_codes(y, s_ref)))
+    # module form, and equality with the unfused modules on the device (same kernels for the quantiser)
+    from quarot_b200.nn.fused import RMSNormQuantizer
+    fused = RMSNormQuantizer(n, 1e-5, clip)(x.to(DEV))
+    q2, s2, _ = qb.rmsnorm_quant(x.to(DEV), n, 1e-5, clip)
+    assert torch.equal(fused.quantized_x.cpu(), q) and torch.equal(q2.cpu(), q)
+    assert fused.scales_x.shape == (rows, 1)
+

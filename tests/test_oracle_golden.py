@@ -109,3 +109,19 @@ def test_linear_forward_shapes():
     ws = torch.rand(24, 1).half() * 0.01 + 0.005
     r = O.linear4bit_forward(x, w, ws, hadamard_dim=128)
     assert r["out"].shape == (6, 24) and r["packed"].shape == (6, 64) and r["acc"].dtype == torch.int32
+
+
+def test_rmsnorm_bit_exact_vs_upstream(golden):
+    g = golden["rmsnorm"]
+    for tag in ("a", "b", "c", "d"):
+        x = torch.from_numpy(g[tag + "_x"])
+        y = O.rmsnorm_fp16(x, x.shape[-1], 1e-5)
+        assert torch.equal(y.view(torch.int16), torch.from_numpy(g[tag + "_y"]).view(torch.int16)), tag
+
+
+def test_swiglu_is_the_fp16_product_of_torch():
+    gen = torch.Generator().manual_seed(3)
+    g = (torch.randn(64, 256, generator=gen) * 3).half()
+    u = (torch.randn(64, 256, generator=gen) * 3).half()
+    assert torch.equal(O.swiglu_fp16(g, u), torch.nn.functional.silu(g) * u)
+

@@ -149,3 +149,26 @@ def test_synth_distributions():
     u = FQ.unpack_i4(w)
     assert int(u.min()) == -8 and int(u.max()) == 7
     assert torch.equal(synth.activations(64, 512, seed=7), x)
+
+
+def test_gate_up_interleave_layout():
+    """Operand layout of the SwiGLU GEMM: groups of 128 gate rows alternate with the same 128 up rows."""
+    I = 384
+    gate = torch.arange(I).view(I, 1).repeat(1, 3)
+    up = gate + 10000
+    both = quarot_b200.interleave_gate_up(gate, up)
+    assert both.shape == (2 * I, 3)
+    for t in range(I // 128):
+        assert torch.equal(both[256 * t:256 * t + 128], gate[128 * t:128 * (t + 1)])
+        assert torch.equal(both[256 * t + 128:256 * t + 256], up[128 * t:128 * (t + 1)])
+    with pytest.raises(ValueError):
+        quarot_b200.interleave_gate_up(gate[:100], up[:100])
+
+
+def test_new_entry_points_validate_arguments_without_gpu():
+    lib = _lib.lib
+    assert lib.qr_rmsnorm_quant_i4(None, 0, 4096, 4096, 4096, 1e-5, 1.0, None, None, None, None) == 0
+    assert lib.qr_rmsnorm_quant_i4(None, 4, 4096, 4096, 4096, 1e-5, 1.0, None, None, None, None) == -1
+    assert lib.qr_linear_i4_f16_outs(None, None, None, None, None, 256, 256, 256, None, 1, 256, None) == -1
+    assert "outputs" in _lib.last_error()
+
