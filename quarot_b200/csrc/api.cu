@@ -102,7 +102,7 @@ int qr_debug_set_trace(void* device_buffer) {
 
 int qr_set_tuning(const char* key, int value) {
   static const char* known[] = {"gemm_bn", "gemm_pst", "gemm_ist", "gemm_acc", "gemm_grid",
-                                "gemm_swap_max_m", "gemm_splitk", "gemm_2sm", "gemm_ts", "gemm_sync", "gemm_debug", "gemm_tma_out", "pdl", "hadq_debug", "hadq_path", "hadq_tc", nullptr};
+                                "gemm_swap_max_m", "gemm_splitk", "gemm_2sm", "gemm_ts", "gemm_sync", "gemm_debug", "gemm_tma_out", "gemv_max_m", "pdl", "hadq_debug", "hadq_path", "hadq_tc", nullptr};
   if (!key) return qr::fail(QR_EINVAL, "qr_set_tuning: null key");
   for (int i = 0; known[i]; ++i) {
     if (strcmp(known[i], key) == 0) {

@@ -1474,6 +1474,10 @@ static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t*
 // layout and is cleared before every call instead.)
 constexpr size_t kWsCounterRegion = 64u << 10;
 
+// weight-streaming kernel for M <= 8 (gemv_i4.cu)
+int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                   const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st);
+
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
@@ -1563,6 +1567,11 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
     }
     if (bn == 128) return launch_gemm<128, 4, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
     return launch_gemm<64, 6, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
+  }
+  // a handful of token rows: one pass over the weights on the CUDA cores, no tensor-core fixed costs
+  if (M <= tuning("gemv_max_m", 8)) {
+    rc = launch_gemv_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
+    if (rc != QR_EUNSUPPORTED) return rc;
   }
   // decode-sized M: weights fill the MMA rows, tokens are the MMA columns; with a scratch buffer the K
   // loop of a tile is split over several CTAs so that all SMs stream weights

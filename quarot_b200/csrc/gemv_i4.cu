@@ -1,0 +1,168 @@
+// Kernel (b) for a handful of token rows (M <= 8, single-sequence decode): a weight-streaming int4 GEMV on the
+// CUDA cores.  At this size the tensor-core kernel is all fixed cost (tensor-memory set-up, pipeline fill,
+// split-K reduction) while the work is one pass over the packed weights, so the only thing that matters is
+// keeping enough 16-byte weight loads in flight to saturate HBM.
+//
+// A warp owns two output channels at a time.  Lane l reads the 16-byte chunks l, l + 32, ... of both weight rows
+// (coalesced 512 bytes per row and step, streamed past L1), widens every packed word into two int8x4 words with
+// the same x16 trick as the GEMM ((w << 4) & 0xF0F0F0F0 = even elements, w & 0xF0F0F0F0 = odd elements, each
+// byte = 16 x the 4-bit value with its sign) and feeds dp4a against the token rows, which sit packed in shared
+// memory and are widened the same way.  The int32 sums are exactly 256 x the dot products; after a warp-shuffle
+// reduction the epilogue applies the arithmetic of the GEMM epilogue (float(acc) * (s_row * s_col), rounded to
+// fp16, bias added in fp16), so the results are bit-identical to the tensor-core path.
+#include "common.cuh"
+
+namespace qr {
+
+struct GemvParams {
+  const uint8_t* A;      // [M, K/2] packed token rows
+  const uint8_t* B;      // [N, K/2] packed weights
+  const __half* sA;      // [M] or null (int32 mode)
+  const __half* sB;      // [N] or null
+  const __half* bias;    // [N] or null
+  void* out;             // [M, N] fp16 (ldo) or int32
+  int64_t ldo;
+  int M, N, K;
+};
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvRows = 2;     // output channels per warp and pass
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+template <int MT, bool F16>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_i4_kernel(const GemvParams p) {
+  extern __shared__ __align__(16) unsigned char smem_a[];      // MT x K/2 packed token rows (zero rows beyond M)
+  const int kbytes = p.K >> 1;
+  const int nchunks = kbytes >> 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < MT * nchunks; i += kGemvThreads) {
+    const int m = i / nchunks, c = i - m * nchunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m < p.M) v = *reinterpret_cast<const uint4*>(p.A + (size_t)m * kbytes + (size_t)c * 16);
+    *reinterpret_cast<uint4*>(smem_a + (size_t)i * 16) = v;
+  }
+  __syncthreads();
+
+  const int warps_total = gridDim.x * (kGemvThreads / 32);
+  const int npairs = (p.N + kGemvRows - 1) / kGemvRows;
+  for (int pair = blockIdx.x * (kGemvThreads / 32) + warp; pair < npairs; pair += warps_total) {
+    const int n0 = pair * kGemvRows;
+    const bool two = n0 + 1 < p.N;
+    const uint8_t* w0 = p.B + (size_t)n0 * kbytes;
+    const uint8_t* w1 = p.B + (size_t)(two ? n0 + 1 : n0) * kbytes;
+    int acc[kGemvRows][MT];
+#pragma unroll
+    for (int r = 0; r < kGemvRows; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) acc[r][m] = 0;
+
+    // two chunks per row in flight per lane and step
+#pragma unroll 1
+    for (int c = lane; c < nchunks; c += 64) {
+      const bool second = c + 32 < nchunks;
+      uint4 w[kGemvRows][2];
+      w[0][0] = ld_stream16(w0 + (size_t)c * 16);
+      w[1][0] = ld_stream16(w1 + (size_t)c * 16);
+      w[0][1] = second ? ld_stream16(w0 + (size_t)(c + 32) * 16) : make_uint4(0, 0, 0, 0);
+      w[1][1] = second ? ld_stream16(w1 + (size_t)(c + 32) * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        if (h == 1 && !second) break;
+        const int cc = c + 32 * h;
+        const uint32_t* wr0 = reinterpret_cast<const uint32_t*>(&w[0][h]);
+        const uint32_t* wr1 = reinterpret_cast<const uint32_t*>(&w[1][h]);
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          const uint4 a = *reinterpret_cast<const uint4*>(smem_a + ((size_t)m * nchunks + cc) * 16);
+          const uint32_t* ar = reinterpret_cast<const uint32_t*>(&a);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int a_lo = (int)((ar[q] << 4) & 0xF0F0F0F0u), a_hi = (int)(ar[q] & 0xF0F0F0F0u);
+            acc[0][m] = __dp4a((int)((wr0[q] << 4) & 0xF0F0F0F0u), a_lo, acc[0][m]);
+            acc[0][m] = __dp4a((int)(wr0[q] & 0xF0F0F0F0u), a_hi, acc[0][m]);
+            acc[1][m] = __dp4a((int)((wr1[q] << 4) & 0xF0F0F0F0u), a_lo, acc[1][m]);
+            acc[1][m] = __dp4a((int)(wr1[q] & 0xF0F0F0F0u), a_hi, acc[1][m]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kGemvRows; ++r)
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], o);
+    // lane m < M writes row m of both channels
+    if (lane < p.M) {
+#pragma unroll
+      for (int r = 0; r < kGemvRows; ++r) {
+        if (r == 1 && !two) break;
+        const int n = n0 + r;
+        int v = 0;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+          if (m == lane) v = acc[r][m];
+        if (F16) {
+          const float sc = __half2float(p.sA[lane]) * __half2float(p.sB[n]);
+          __half o = __float2half_rn((float)(v >> 8) * sc);
+          if (p.bias) o = __hadd(o, p.bias[n]);
+          reinterpret_cast<__half*>(p.out)[(size_t)lane * p.ldo + n] = o;
+        } else {
+          reinterpret_cast<int32_t*>(p.out)[(size_t)lane * p.ldo + n] = v >> 8;
+        }
+      }
+    }
+  }
+}
+
+template <int MT, bool F16>
+static int launch_gemv_mt(const GemvParams& p, cudaStream_t st) {
+  const size_t smem = (size_t)MT * (p.K >> 1);
+  auto kern = gemv_i4_kernel<MT, F16>;
+  static thread_local size_t configured[64] = {0};
+  int dev = 0;
+  QR_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev >= 64 || configured[dev] < smem)) {
+    QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = smem;
+  }
+  // enough resident warps to keep HBM busy; every warp takes pairs of output channels round-robin
+  int per_sm = (int)((200 * 1024) / (smem + 1024));
+  if (per_sm > 4) per_sm = 4;
+  if (per_sm < 1) per_sm = 1;
+  int64_t grid = (int64_t)num_sms() * per_sm;
+  const int64_t need = ((int64_t)(p.N + kGemvRows - 1) / kGemvRows + (kGemvThreads / 32) - 1) / (kGemvThreads / 32);
+  if (grid > need) grid = need;
+  QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGemvThreads), smem, st, false, p));
+  return QR_OK;
+}
+
+// Returns QR_EUNSUPPORTED when the shape is not one this kernel serves (the caller then takes the tensor-core path).
+int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                   const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st) {
+  if (M < 1 || M > 8 || K % 32 != 0 || K > 65536 || N > (1 << 30)) return QR_EUNSUPPORTED;
+  if ((size_t)8 * (K >> 1) > 200 * 1024) return QR_EUNSUPPORTED;
+  GemvParams p;
+  p.A = A; p.B = B; p.sA = reinterpret_cast<const __half*>(sA); p.sB = reinterpret_cast<const __half*>(sB);
+  p.bias = reinterpret_cast<const __half*>(bias); p.out = out; p.ldo = ldo;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  if (f16) {
+    if (M == 1) return launch_gemv_mt<1, true>(p, st);
+    if (M == 2) return launch_gemv_mt<2, true>(p, st);
+    if (M <= 4) return launch_gemv_mt<4, true>(p, st);
+    return launch_gemv_mt<8, true>(p, st);
+  }
+  if (M == 1) return launch_gemv_mt<1, false>(p, st);
+  if (M == 2) return launch_gemv_mt<2, false>(p, st);
+  if (M <= 4) return launch_gemv_mt<4, false>(p, st);
+  return launch_gemv_mt<8, false>(p, st);
+}
+
+}  // namespace qr

@@ -225,22 +225,48 @@ def test_decode_split_k_matches_single_pass(M, N, K):
     need = _lib.lib.qr_linear_workspace_bytes(M, N, K)
     assert need > 0
     ad, wd, sxd, swd, bd = a.to(DEV), w.to(DEV), sx.to(DEV), sw.to(DEV), bias.to(DEV)
-    one = qb.linear_i4(ad, sxd, wd, swd, bd, use_workspace=False)
-    for _ in range(3):   # repeated launches: the arrival counters must come back to zero
-        split = qb.linear_i4(ad, sxd, wd, swd, bd)
-        assert torch.equal(split, one)
     ref = O.sym_dequant_fp32(O.matmul_i4(a, w), sx, sw).half() + bias
-    assert torch.equal(one.cpu(), ref)
+    # M <= 8 is normally served by the weight-streaming kernel; gemv_max_m = 0 sends it through the tensor cores
+    for gemv_max_m in (8, 0):
+        _lib.set_tuning("gemv_max_m", gemv_max_m)
+        try:
+            one = qb.linear_i4(ad, sxd, wd, swd, bd, use_workspace=False)
+            for _ in range(3):   # repeated launches: the arrival counters must come back to zero
+                split = qb.linear_i4(ad, sxd, wd, swd, bd)
+                assert torch.equal(split, one)
+        finally:
+            _lib.set_tuning("gemv_max_m", 8)
+        assert torch.equal(one.cpu(), ref)
+    assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (2, 1000, 2048), (3, 12288, 4096), (5, 4096, 11008), (8, 22016, 4096),
+                                   (7, 33, 64), (8, 8192, 28672), (1, 1, 64)])
+def test_weight_streaming_kernel_for_a_few_rows(M, N, K):
+    """M <= 8: one pass over the packed weights with dp4a on the CUDA cores; exact accumulators and the same
+    dequantisation arithmetic as the tensor-core kernels."""
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a, w = _rand_packed(M, K, 61), _rand_packed(N, K, 62)
+    sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand(N, generator=g) * 0.015 + 0.005).half()
+    bias = (torch.randn(N, generator=g) * 0.5).half()
+    acc = O.matmul_i4(a, w)
+    ad, wd = a.to(DEV), w.to(DEV)
+    assert torch.equal(qb.matmul(ad, wd).cpu(), acc)
+    out = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), bias.to(DEV))
+    assert torch.equal(out.cpu(), O.sym_dequant_fp32(acc, sx, sw).half() + bias)
+    out2 = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV))
+    assert torch.equal(out2.cpu(), O.sym_dequant_fp32(acc, sx, sw).half())
     assert _lib.kernel_status() == 0
 
 
 def test_workspace_argument_errors():
-    a, w = _rand_packed(8, 4096, 1).to(DEV), _rand_packed(4096, 4096, 2).to(DEV)
-    sx, sw = torch.ones(8, device=DEV).half(), torch.ones(4096, device=DEV).half()
-    out = torch.empty(8, 4096, device=DEV, dtype=torch.float16)
-    need = _lib.lib.qr_linear_workspace_bytes(8, 4096, 4096)
+    a, w = _rand_packed(16, 4096, 1).to(DEV), _rand_packed(4096, 4096, 2).to(DEV)
+    sx, sw = torch.ones(16, device=DEV).half(), torch.ones(4096, device=DEV).half()
+    out = torch.empty(16, 4096, device=DEV, dtype=torch.float16)
+    need = _lib.lib.qr_linear_workspace_bytes(16, 4096, 4096)
     small = torch.zeros(256, dtype=torch.uint8, device=DEV)
-    rc = _lib.lib.qr_linear_i4_f16_ws(a.data_ptr(), sx.data_ptr(), w.data_ptr(), sw.data_ptr(), None, 8, 4096, 4096,
+    rc = _lib.lib.qr_linear_i4_f16_ws(a.data_ptr(), sx.data_ptr(), w.data_ptr(), sw.data_ptr(), None, 16, 4096, 4096,
                                       out.data_ptr(), 4096, small.data_ptr(), small.numel(), None)
     assert rc == -1 and "workspace" in _lib.last_error() and need > 256
     assert _lib.lib.qr_linear_workspace_bytes(2048, 4096, 4096) == 0     # prefill shapes never split
