@@ -3,7 +3,7 @@
 // split-K reduction) while the work is one pass over the packed weights, so the only thing that matters is
 // keeping enough 16-byte weight loads in flight to saturate HBM.
 //
-// A warp owns two output channels at a time.  Lane l reads the 16-byte chunks l, l + 32, ... of both weight rows
+// A warp owns one or two output channels at a time.  Lane l reads the 16-byte chunks l, l + 32, ... of its weight rows
 // (coalesced 512 bytes per row and step, streamed past L1), widens every packed word into two int8x4 words with
 // the same x16 trick as the GEMM ((w << 4) & 0xF0F0F0F0 = even elements, w & 0xF0F0F0F0 = odd elements, each
 // byte = 16 x the 4-bit value with its sign) and feeds dp4a against the token rows, which sit packed in shared
@@ -26,7 +26,6 @@ struct GemvParams {
 };
 
 constexpr int kGemvThreads = 256;
-constexpr int kGemvRows = 2;     // output channels per warp and pass
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
@@ -35,9 +34,12 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return v;
 }
 
-template <int MT, bool F16>
+// MT: token rows held per warp (M rounded up), ROWS: output channels a warp works on at a time (two share the
+// widening of the token rows; one gives twice as many warps when there are few output channels).
+template <int MT, int ROWS, bool F16>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_i4_kernel(const GemvParams p) {
+  constexpr int kGemvRows = ROWS;
   extern __shared__ __align__(16) unsigned char smem_a[];      // MT x K/2 packed token rows (zero rows beyond M)
   const int kbytes = p.K >> 1;
   const int nchunks = kbytes >> 4;
@@ -50,34 +52,54 @@ gemv_i4_kernel(const GemvParams p) {
   }
   __syncthreads();
 
+  // The work of a warp is the flat sequence (channel pair, k step); the weight chunks of step t + 1 are requested
+  // before step t is computed, also across pair boundaries, so that every lane always has up to eight 16-byte
+  // loads in flight.
   const int warps_total = gridDim.x * (kGemvThreads / 32);
+  const int warp_id = blockIdx.x * (kGemvThreads / 32) + warp;
   const int npairs = (p.N + kGemvRows - 1) / kGemvRows;
-  for (int pair = blockIdx.x * (kGemvThreads / 32) + warp; pair < npairs; pair += warps_total) {
-    const int n0 = pair * kGemvRows;
-    const bool two = n0 + 1 < p.N;
-    const uint8_t* w0 = p.B + (size_t)n0 * kbytes;
-    const uint8_t* w1 = p.B + (size_t)(two ? n0 + 1 : n0) * kbytes;
-    int acc[kGemvRows][MT];
-#pragma unroll
-    for (int r = 0; r < kGemvRows; ++r)
-#pragma unroll
-      for (int m = 0; m < MT; ++m) acc[r][m] = 0;
+  const int steps = (nchunks + 63) >> 6;                       // 64 chunks (2 per lane) per step
+  const int my_pairs = warp_id < npairs ? (npairs - warp_id + warps_total - 1) / warps_total : 0;
+  const int total = my_pairs * steps;
 
-    // two chunks per row in flight per lane and step
-#pragma unroll 1
-    for (int c = lane; c < nchunks; c += 64) {
-      const bool second = c + 32 < nchunks;
-      uint4 w[kGemvRows][2];
-      w[0][0] = ld_stream16(w0 + (size_t)c * 16);
-      w[1][0] = ld_stream16(w1 + (size_t)c * 16);
-      w[0][1] = second ? ld_stream16(w0 + (size_t)(c + 32) * 16) : make_uint4(0, 0, 0, 0);
-      w[1][1] = second ? ld_stream16(w1 + (size_t)(c + 32) * 16) : make_uint4(0, 0, 0, 0);
+  auto row_ptr = [&](int t, int r) {
+    const int pair = warp_id + (t / steps) * warps_total;
+    int n = pair * kGemvRows + r;
+    if (n >= p.N) n = p.N - 1;
+    return p.B + (size_t)n * kbytes;
+  };
+  auto load_step = [&](int t, uint4 (&w)[kGemvRows][2]) {
+    const int c = lane + ((t % steps) << 6);
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (h == 1 && !second) break;
-        const int cc = c + 32 * h;
-        const uint32_t* wr0 = reinterpret_cast<const uint32_t*>(&w[0][h]);
-        const uint32_t* wr1 = reinterpret_cast<const uint32_t*>(&w[1][h]);
+    for (int r = 0; r < kGemvRows; ++r) {
+      const uint8_t* rp = row_ptr(t, r);
+      w[r][0] = (c < nchunks) ? ld_stream16(rp + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+      w[r][1] = (c + 32 < nchunks) ? ld_stream16(rp + (size_t)(c + 32) * 16) : make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  int acc[kGemvRows][MT];
+#pragma unroll
+  for (int r = 0; r < kGemvRows; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[r][m] = 0;
+  // With one or two token rows the registers allow requesting step t + 1 before step t is computed; with more
+  // rows (more accumulators) the extra registers cost more occupancy than the prefetch gains (measured).
+  constexpr bool kPrefetch = (MT <= 2);
+  uint4 cur[kGemvRows][2], nxt[kGemvRows][2];
+  if (kPrefetch && total > 0) load_step(0, cur);
+#pragma unroll 1
+  for (int t = 0; t < total; ++t) {
+    if (kPrefetch) {
+      if (t + 1 < total) load_step(t + 1, nxt);
+    } else {
+      load_step(t, cur);
+    }
+    const int c = lane + ((t % steps) << 6);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int cc = c + 32 * h;
+      if (cc < nchunks) {
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
           const uint4 a = *reinterpret_cast<const uint4*>(smem_a + ((size_t)m * nchunks + cc) * 16);
@@ -85,47 +107,62 @@ gemv_i4_kernel(const GemvParams p) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const int a_lo = (int)((ar[q] << 4) & 0xF0F0F0F0u), a_hi = (int)(ar[q] & 0xF0F0F0F0u);
-            acc[0][m] = __dp4a((int)((wr0[q] << 4) & 0xF0F0F0F0u), a_lo, acc[0][m]);
-            acc[0][m] = __dp4a((int)(wr0[q] & 0xF0F0F0F0u), a_hi, acc[0][m]);
-            acc[1][m] = __dp4a((int)((wr1[q] << 4) & 0xF0F0F0F0u), a_lo, acc[1][m]);
-            acc[1][m] = __dp4a((int)(wr1[q] & 0xF0F0F0F0u), a_hi, acc[1][m]);
+#pragma unroll
+            for (int r = 0; r < kGemvRows; ++r) {
+              const uint32_t wv = reinterpret_cast<const uint32_t*>(&cur[r][h])[q];
+              acc[r][m] = __dp4a((int)((wv << 4) & 0xF0F0F0F0u), a_lo, acc[r][m]);
+              acc[r][m] = __dp4a((int)(wv & 0xF0F0F0F0u), a_hi, acc[r][m]);
+            }
           }
         }
       }
     }
+    if ((t + 1) % steps == 0) {
+      // the pair is complete: reduce over the lanes, dequantise, store, start the next pair from zero
+      const int n0 = (warp_id + (t / steps) * warps_total) * kGemvRows;
+      const bool two = n0 + 1 < p.N;
 #pragma unroll
-    for (int r = 0; r < kGemvRows; ++r)
-#pragma unroll
-      for (int m = 0; m < MT; ++m)
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], o);
-    // lane m < M writes row m of both channels
-    if (lane < p.M) {
-#pragma unroll
-      for (int r = 0; r < kGemvRows; ++r) {
-        if (r == 1 && !two) break;
-        const int n = n0 + r;
-        int v = 0;
+      for (int r = 0; r < kGemvRows; ++r)
 #pragma unroll
         for (int m = 0; m < MT; ++m)
-          if (m == lane) v = acc[r][m];
-        if (F16) {
-          const float sc = __half2float(p.sA[lane]) * __half2float(p.sB[n]);
-          __half o = __float2half_rn((float)(v >> 8) * sc);
-          if (p.bias) o = __hadd(o, p.bias[n]);
-          reinterpret_cast<__half*>(p.out)[(size_t)lane * p.ldo + n] = o;
-        } else {
-          reinterpret_cast<int32_t*>(p.out)[(size_t)lane * p.ldo + n] = v >> 8;
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) acc[r][m] += __shfl_xor_sync(0xffffffffu, acc[r][m], o);
+      if (lane < p.M) {      // lane m writes row m of both channels
+#pragma unroll
+        for (int r = 0; r < kGemvRows; ++r) {
+          if (r == 1 && !two) break;
+          const int n = n0 + r;
+          int v = 0;
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m == lane) v = acc[r][m];
+          if (F16) {
+            const float sc = __half2float(p.sA[lane]) * __half2float(p.sB[n]);
+            __half o = __float2half_rn((float)(v >> 8) * sc);
+            if (p.bias) o = __hadd(o, p.bias[n]);
+            reinterpret_cast<__half*>(p.out)[(size_t)lane * p.ldo + n] = o;
+          } else {
+            reinterpret_cast<int32_t*>(p.out)[(size_t)lane * p.ldo + n] = v >> 8;
+          }
         }
       }
+#pragma unroll
+      for (int r = 0; r < kGemvRows; ++r)
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[r][m] = 0;
+    }
+    if (kPrefetch) {
+#pragma unroll
+      for (int r = 0; r < kGemvRows; ++r) { cur[r][0] = nxt[r][0]; cur[r][1] = nxt[r][1]; }
     }
   }
 }
 
-template <int MT, bool F16>
+template <int MT, int ROWS, bool F16>
 static int launch_gemv_mt(const GemvParams& p, cudaStream_t st) {
+  constexpr int kGemvRows = ROWS;
   const size_t smem = (size_t)MT * (p.K >> 1);
-  auto kern = gemv_i4_kernel<MT, F16>;
+  auto kern = gemv_i4_kernel<MT, ROWS, F16>;
   static thread_local size_t configured[64] = {0};
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
@@ -154,15 +191,15 @@ int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int
   p.bias = reinterpret_cast<const __half*>(bias); p.out = out; p.ldo = ldo;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
   if (f16) {
-    if (M == 1) return launch_gemv_mt<1, true>(p, st);
-    if (M == 2) return launch_gemv_mt<2, true>(p, st);
-    if (M <= 4) return launch_gemv_mt<4, true>(p, st);
-    return launch_gemv_mt<8, true>(p, st);
+    if (M == 1) return launch_gemv_mt<1, 2, true>(p, st);
+    if (M == 2) return launch_gemv_mt<2, 2, true>(p, st);
+    if (M <= 4) return launch_gemv_mt<4, 2, true>(p, st);
+    return launch_gemv_mt<8, 2, true>(p, st);
   }
-  if (M == 1) return launch_gemv_mt<1, false>(p, st);
-  if (M == 2) return launch_gemv_mt<2, false>(p, st);
-  if (M <= 4) return launch_gemv_mt<4, false>(p, st);
-  return launch_gemv_mt<8, false>(p, st);
+  if (M == 1) return launch_gemv_mt<1, 2, false>(p, st);
+  if (M == 2) return launch_gemv_mt<2, 2, false>(p, st);
+  if (M <= 4) return launch_gemv_mt<4, 2, false>(p, st);
+  return launch_gemv_mt<8, 2, false>(p, st);
 }
 
 }  // namespace qr
