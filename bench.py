@@ -39,7 +39,7 @@ WORKLOADS = {
     "config0": ("CONFIG0", 2048),
     "llama2_7b_decode": ("LLAMA2_7B", 32),
     "llama2_70b_prefill": ("LLAMA2_70B", 4096),
-    # BASELINE config 4: the two 70B MLP linears with their output channels split over the ranks and an
+    # the two 70B MLP linears with their output channels split over the ranks and an
     # all-gather of the fp16 result; every rank sees all token rows (use --tokens to sweep M)
     "llama2_70b_mlp_colsplit": ("LLAMA2_70B_MLP", 4096),
     # the MLP block around the path (first of the rows that come after it): quantise -> gate/up -> SiLU product ->

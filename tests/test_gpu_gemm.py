@@ -190,7 +190,7 @@ def test_from_float_roundtrip():
 
 
 def test_full_size_config0_properties():
-    """BASELINE config 0 at full size: checksum identity over all 8.4 M accumulators plus sampled rows."""
+    """The single-linear configuration (M 2048, K 4096, N 4096) at full size: checksum identity over all 8.4 M accumulators plus sampled rows."""
     M, K, N = 2048, 4096, 4096
     x = synth.activations(M, K, seed=1234).to(DEV)
     w, sw = synth.weights(N, K, seed=4321)
