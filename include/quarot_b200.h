@@ -174,6 +174,17 @@ int qr_linear_i4_f16_outs(const uint8_t* A, const void* sA, const uint8_t* B, co
 int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
                             int64_t M, int64_t N2, int64_t K, void* out, int64_t ldo, void* stream);
 
+/* Quantizer.forward + Linear4bit.forward (quarot/nn/quantization.py:9-13, quarot/nn/linear.py:42-56) in one
+ * launch for at most 8 token rows (single-sequence decode): every CTA of the weight-streaming kernel quantises the
+ * rows itself (same scales and codes as qr_hadamard_quant_i4 with K = 0), so the separate quantiser launch and
+ * the packed activations disappear.  Same result, bit for bit, as the two calls.
+ *   x [M, K] fp16 with row stride ldx (ldx % 8 == 0, 16-byte aligned), clip = Quantizer.input_clip_ratio,
+ *   B [N, K/2] int4 packed, sB [N] fp16, bias [N] fp16 or NULL, out [M, N] fp16 with row stride ldo.
+ * M > 8: QR_EUNSUPPORTED.  No upstream counterpart. */
+int qr_quant_linear_i4_f16(const void* x, int64_t ldx, float clip, const uint8_t* B, const void* sB,
+                           const void* bias, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                           void* stream);
+
 /* Decode-sized M (M <= 64) is bound by streaming the weights; with few output tiles a single pass
  * leaves most SMs idle, so the K loop of every tile can be split over several CTAs that meet in a
  * caller-provided scratch buffer (int32 partial tiles + one arrival counter per tile; the split that

@@ -12,14 +12,14 @@ import sys
 
 from . import _lib
 from ._ops import (matmul, sym_quant, sym_dequant, PackedQuantizedTensor, hadamard, hadamard_quant,
-                   linear_i4, linear_i4_outs, linear_i4_swiglu, interleave_gate_up, rmsnorm_quant,
+                   linear_i4, linear_i4_outs, linear_i4_swiglu, interleave_gate_up, rmsnorm_quant, quant_linear_i4,
                    flatten_last_dim_and_return_shape)
 from . import functional
 from . import nn
 from . import transformers
 
 __all__ = ["matmul", "sym_quant", "sym_dequant", "PackedQuantizedTensor",
-           "hadamard_quant", "hadamard", "linear_i4", "linear_i4_outs", "linear_i4_swiglu", "interleave_gate_up", "rmsnorm_quant", "install_as_quarot"]
+           "hadamard_quant", "hadamard", "linear_i4", "linear_i4_outs", "linear_i4_swiglu", "interleave_gate_up", "rmsnorm_quant", "quant_linear_i4", "install_as_quarot"]
 
 
 def install_as_quarot():

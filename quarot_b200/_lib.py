@@ -36,6 +36,7 @@ SIGNATURES = {
     "qr_linear_i4_f16_outs": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, ctypes.POINTER(ctypes.c_void_p), _int, _i64, _vp]),
     "qr_linear_i4_swiglu_f16": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "qr_rmsnorm_quant_i4": (_int, [_vp, _i64, _i64, _i64, _i64, ctypes.c_float, ctypes.c_float, _vp, _vp, _vp, _vp]),
+    "qr_quant_linear_i4_f16": (_int, [_vp, _i64, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "qr_linear_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
     "qr_linear_i4_f16_static": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "qr_linear_i4_f16_ws": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, ctypes.c_size_t, _vp]),

@@ -280,3 +280,24 @@ def rmsnorm_quant(x, mean_dim, eps=1e-5, clip=1.0, return_y=False):
         _lib.check(rc, "rmsnorm_quant")
     return (q.view(*shape_excl_last, n // 2), s, y.view(*shape_excl_last, n) if return_y else None)
 
+
+def quant_linear_i4(x, weight, weight_scales, bias=None, clip=1.0, out=None):
+    """Quantizer + Linear4bit in one launch for at most 8 token rows (x fp16 [..., K] -> fp16 [..., N])."""
+    assert x.dtype == torch.float16
+    x2, shape_excl_last = flatten_last_dim_and_return_shape(x)
+    sw = weight_scales.view(-1)
+    dev = _check_cuda_contig("quant_linear_i4", x=x2, weight=weight, weight_scales=sw, bias=bias)
+    M, K = x2.shape
+    N = weight.shape[0]
+    if weight.shape[1] * 2 != K or sw.shape[0] != N:
+        raise RuntimeError("quant_linear_i4: operand sizes do not match")
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.float16, device=dev)
+        ldo = out.stride(0) if M > 1 else max(out.stride(0), N)
+        rc = _lib_c.qr_quant_linear_i4_f16(x2.data_ptr(), x2.stride(0) if M > 1 else max(x2.stride(0), K), float(clip),
+                                           weight.data_ptr(), sw.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                           M, N, K, out.data_ptr(), ldo, _stream(dev))
+        _lib.check(rc, "quant_linear_i4")
+    return out.view(*shape_excl_last, N) if out.is_contiguous() else out
+

@@ -1476,7 +1476,8 @@ constexpr size_t kWsCounterRegion = 64u << 10;
 
 // weight-streaming kernel for M <= 8 (gemv_i4.cu)
 int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
-                   const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st);
+                   const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st,
+                   const void* x = nullptr, int64_t ldx = 0, float clip = 1.0f);
 
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,

@@ -23,6 +23,10 @@ struct GemvParams {
   void* out;             // [M, N] fp16 (ldo) or int32
   int64_t ldo;
   int M, N, K;
+  // fused quantiser: when x is set, A and sA are ignored and every CTA quantises the token rows itself
+  const __half* x;       // [M, K] fp16 token rows (row stride ldx), or null
+  int64_t ldx;
+  float clip;
 };
 
 constexpr int kGemvThreads = 256;
@@ -41,14 +45,59 @@ __global__ void __launch_bounds__(kGemvThreads)
 gemv_i4_kernel(const GemvParams p) {
   constexpr int kGemvRows = ROWS;
   extern __shared__ __align__(16) unsigned char smem_a[];      // MT x K/2 packed token rows (zero rows beyond M)
+  __shared__ float s_red[kGemvThreads / 32];
+  __shared__ float s_scale[MT];                                // per-token scales of the token rows
   const int kbytes = p.K >> 1;
   const int nchunks = kbytes >> 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < MT * nchunks; i += kGemvThreads) {
-    const int m = i / nchunks, c = i - m * nchunks;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (m < p.M) v = *reinterpret_cast<const uint4*>(p.A + (size_t)m * kbytes + (size_t)c * 16);
-    *reinterpret_cast<uint4*>(smem_a + (size_t)i * 16) = v;
+  if (p.x == nullptr) {
+    for (int i = threadIdx.x; i < MT * nchunks; i += kGemvThreads) {
+      const int m = i / nchunks, c = i - m * nchunks;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (m < p.M) v = *reinterpret_cast<const uint4*>(p.A + (size_t)m * kbytes + (size_t)c * 16);
+      *reinterpret_cast<uint4*>(smem_a + (size_t)i * 16) = v;
+    }
+    if (F16 && threadIdx.x < MT) s_scale[threadIdx.x] = threadIdx.x < p.M ? __half2float(p.sA[threadIdx.x]) : 0.0f;
+  } else {
+    // Quantizer fused in: per token row absmax -> s = fp16(fp16(absmax / 7) * clip) -> int4 codes, exactly as the
+    // stand-alone quantiser does it; every CTA repeats this for the (at most eight) rows, which costs less than a
+    // launch.  A 16-byte packed chunk comes from four 16-byte groups of eight fp16 values.
+    const int ngroups = p.K >> 3;
+    for (int m = 0; m < MT; ++m) {
+      float s = 0.0f;
+      if (m < p.M) {
+        const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx);
+        __half2 mx = __float2half2_rn(0.0f);
+        for (int g = threadIdx.x; g < ngroups; g += kGemvThreads) {
+          const uint4 v = __ldg(xr + g);
+          const __half2* h = reinterpret_cast<const __half2*>(&v);
+          mx = __hmax2(mx, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
+        }
+        const float2 mf = __half22float2(mx);
+        float a = fmaxf(mf.x, mf.y);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        if (lane == 0) s_red[warp] = a;
+        __syncthreads();
+        a = (lane < kGemvThreads / 32) ? s_red[lane] : 0.0f;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
+        __syncthreads();
+        const __half s7 = __float2half_rn(__fdiv_rn(a, 7.0f));
+        s = __half2float(__float2half_rn(__half2float(s7) * p.clip));
+        const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+        const bool noclamp = clamp_free(s, p.clip);
+        uint32_t* dst = reinterpret_cast<uint32_t*>(smem_a + (size_t)m * kbytes);
+        for (int g = threadIdx.x; g < ngroups; g += kGemvThreads) {
+          const uint4 v = __ldg(xr + g);
+          dst[g] = quant8_words(v.x, v.y, v.z, v.w, s, rcp, noclamp);
+        }
+      } else {
+        uint32_t* dst = reinterpret_cast<uint32_t*>(smem_a + (size_t)m * kbytes);
+        for (int g = threadIdx.x; g < ngroups; g += kGemvThreads) dst[g] = 0u;
+      }
+      if (threadIdx.x == 0) s_scale[m] = s;
+    }
   }
   __syncthreads();
 
@@ -137,7 +186,7 @@ gemv_i4_kernel(const GemvParams p) {
           for (int m = 0; m < MT; ++m)
             if (m == lane) v = acc[r][m];
           if (F16) {
-            const float sc = __half2float(p.sA[lane]) * __half2float(p.sB[n]);
+            const float sc = s_scale[lane] * __half2float(p.sB[n]);
             __half o = __float2half_rn((float)(v >> 8) * sc);
             if (p.bias) o = __hadd(o, p.bias[n]);
             reinterpret_cast<__half*>(p.out)[(size_t)lane * p.ldo + n] = o;
@@ -183,13 +232,15 @@ static int launch_gemv_mt(const GemvParams& p, cudaStream_t st) {
 
 // Returns QR_EUNSUPPORTED when the shape is not one this kernel serves (the caller then takes the tensor-core path).
 int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
-                   const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st) {
+                   const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st,
+                   const void* x, int64_t ldx, float clip) {
   if (M < 1 || M > 8 || K % 32 != 0 || K > 65536 || N > (1 << 30)) return QR_EUNSUPPORTED;
   if ((size_t)8 * (K >> 1) > 200 * 1024) return QR_EUNSUPPORTED;
   GemvParams p;
   p.A = A; p.B = B; p.sA = reinterpret_cast<const __half*>(sA); p.sB = reinterpret_cast<const __half*>(sB);
   p.bias = reinterpret_cast<const __half*>(bias); p.out = out; p.ldo = ldo;
   p.M = (int)M; p.N = (int)N; p.K = (int)K;
+  p.x = reinterpret_cast<const __half*>(x); p.ldx = ldx; p.clip = clip;
   if (f16) {
     if (M == 1) return launch_gemv_mt<1, 2, true>(p, st);
     if (M == 2) return launch_gemv_mt<2, 2, true>(p, st);
@@ -203,3 +254,20 @@ int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int
 }
 
 }  // namespace qr
+
+extern "C" int qr_quant_linear_i4_f16(const void* x, int64_t ldx, float clip, const uint8_t* B, const void* sB,
+                                      const void* bias, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                                      void* stream) {
+  if (M < 0 || N < 0 || K < 0) return qr::fail(QR_EINVAL, "qr_quant_linear_i4_f16: negative size");
+  if (M == 0 || N == 0) return QR_OK;
+  if (!x || !B || !sB || !out) return qr::fail(QR_EINVAL, "qr_quant_linear_i4_f16: null pointer");
+  if (K == 0 || K % 32 != 0) return qr::fail(QR_EINVAL, "qr_quant_linear_i4_f16: K = %lld must be a positive multiple of 32", (long long)K);
+  if (ldx < K || ldo < N) return qr::fail(QR_EINVAL, "qr_quant_linear_i4_f16: leading dimension too small");
+  if (!qr::aligned16(x) || ldx % 8 != 0 || !qr::aligned16(B))
+    return qr::fail(QR_EALIGN, "qr_quant_linear_i4_f16: x and B must be 16-byte aligned, ldx % 8 == 0");
+  if (M > 8) return qr::fail(QR_EUNSUPPORTED, "qr_quant_linear_i4_f16: at most 8 token rows (use the quantiser and qr_linear_i4_f16)");
+  const int rc = qr::launch_gemv_i4(nullptr, B, M, N, K, out, ldo, nullptr, sB, bias, true, (cudaStream_t)stream, x, ldx, clip);
+  if (rc == QR_EUNSUPPORTED) return qr::fail(QR_EUNSUPPORTED, "qr_quant_linear_i4_f16: K = %lld is too long for this kernel", (long long)K);
+  return rc;
+}
+

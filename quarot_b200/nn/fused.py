@@ -88,3 +88,20 @@ class RMSNormQuantizer(torch.nn.Module):
         q, s, _ = _ops.rmsnorm_quant(x, self.mean_dim, self.eps, self.input_clip_ratio)
         return _ops.PackedQuantizedTensor(q, s.view(x.shape[:-1]).unsqueeze(1))
 
+
+class QuantLinear4bit(torch.nn.Module):
+    """Sequential(Quantizer, Linear4bit) as one module: with one or two token rows (single-sequence decode) the
+    quantiser runs inside the weight-streaming kernel, otherwise the two modules run one after the other (every
+    CTA of the fused kernel quantises all rows itself, which stops paying off at four rows: measured)."""
+
+    def __init__(self, quantizer, linear):
+        super().__init__()
+        self.quantizer, self.linear = quantizer, linear
+
+    def forward(self, x):
+        rows = x.numel() // x.shape[-1]
+        if rows <= 2 and x.dtype == torch.float16:
+            return _ops.quant_linear_i4(x, self.linear.weight, self.linear.weight_scales, self.linear.bias,
+                                        self.quantizer.input_clip_ratio)
+        return self.linear(self.quantizer(x))
+

@@ -352,3 +352,29 @@ def test_swiglu_module_and_small_batches():
         assert torch.equal(fused(xq), want), rows
     assert _lib.kernel_status() == 0
 
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (3, 1000, 2048), (8, 12288, 4096), (5, 512, 11008)])
+@pytest.mark.parametrize("clip", [1.0, 0.9])
+def test_quantizer_inside_the_weight_streaming_kernel(M, N, K, clip):
+    """Quantizer + Linear4bit in one launch (M <= 8): the same bits as the two modules."""
+    from quarot_b200.nn.fused import QuantLinear4bit
+    x = synth.activations(M, K, seed=M + K).to(DEV)
+    x[0, :7] = 0
+    lin = qb.nn.Linear4bit(K, N, bias=True).to(DEV)
+    lin.weight = _rand_packed(N, K, 71).to(DEV)
+    lin.weight_scales = (torch.rand(N, 1) * 0.015 + 0.005).half().to(DEV)
+    lin.bias = torch.randn(N).half().to(DEV)
+    quant = qb.nn.Quantizer(clip)
+    want = lin(quant(x))
+    got = qb.quant_linear_i4(x, lin.weight, lin.weight_scales, lin.bias, clip)
+    assert torch.equal(got, want)
+    assert torch.equal(QuantLinear4bit(quant, lin)(x), want)
+    xq = quant(x)
+    ref = O.sym_dequant_fp32(O.matmul_i4(xq.quantized_x.cpu(), lin.weight.cpu()), xq.scales_x.cpu().view(-1),
+                             lin.weight_scales.cpu()).half() + lin.bias.cpu()
+    assert torch.equal(got.cpu(), ref)
+    # more rows than the fused kernel takes: the module falls back to the two calls
+    xb = synth.activations(9, K, seed=9).to(DEV)
+    assert torch.equal(QuantLinear4bit(quant, lin)(xb), lin(quant(xb)))
+    assert _lib.kernel_status() == 0
+
