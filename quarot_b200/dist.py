@@ -135,9 +135,18 @@ class FusedColumnSplitLinear4bit(ColumnSplitLinear4bit):
         if target.cols != self.out_features or n_loc * self.world != self.out_features:
             raise RuntimeError("FusedColumnSplitLinear4bit: target has %d columns, expected %d" % (target.cols, self.out_features))
         col_bytes = 2 * n_loc * self.rank
+        rows = x.quantized_x.numel() // x.quantized_x.shape[-1]
         target.barrier()          # nobody still reads the previous contents
-        _ops.linear_i4_outs(x.quantized_x, x.scales_x, self.weight, self.weight_scales, self.bias,
-                            [p + col_bytes for p in target.ptrs], target.cols)
+        if rows > 128:
+            _ops.linear_i4_outs(x.quantized_x, x.scales_x, self.weight, self.weight_scales, self.bias,
+                                [p + col_bytes for p in target.ptrs], target.cols)
+        else:
+            # few token rows (served by the decode kernels): the slab is computed locally and copied into the
+            # column block of every rank's matrix
+            local = self.local_forward(x).reshape(rows, n_loc)
+            for g in range(self.world):
+                peer = target.handle.get_buffer(g, (target.rows, target.cols), torch.float16)
+                peer[:rows, self.rank * n_loc:(self.rank + 1) * n_loc].copy_(local)
         target.barrier()          # every rank's slab is in every copy
         return target.local
 
