@@ -10,6 +10,8 @@
 // memory and are widened the same way.  The int32 sums are exactly 256 x the dot products; after a warp-shuffle
 // reduction the epilogue applies the arithmetic of the GEMM epilogue (float(acc) * (s_row * s_col), rounded to
 // fp16, bias added in fp16), so the results are bit-identical to the tensor-core path.
+// (A variant that streamed the weights with cp.async.bulk into a shared-memory ring, one thread issuing and eight
+// warps consuming, was measured at half this kernel's rate -- 1.7 TB/s -- and dropped.)
 #include "common.cuh"
 
 namespace qr {
@@ -38,20 +40,17 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   return v;
 }
 
-// MT: token rows held per warp (M rounded up), ROWS: output channels a warp works on at a time (two share the
-// widening of the token rows; one gives twice as many warps when there are few output channels).
-template <int MT, int ROWS, bool F16>
-__global__ void __launch_bounds__(kGemvThreads)
-gemv_i4_kernel(const GemvParams p) {
-  constexpr int kGemvRows = ROWS;
-  extern __shared__ __align__(16) unsigned char smem_a[];      // MT x K/2 packed token rows (zero rows beyond M)
-  __shared__ float s_red[kGemvThreads / 32];
-  __shared__ float s_scale[MT];                                // per-token scales of the token rows
+// Brings the token rows into shared memory as packed int4 (MT rows of K/2 bytes, zero rows beyond M) together with
+// their per-token scales: either copied from the caller's packed rows, or -- when p.x is set -- quantised here from
+// fp16 (Quantizer fused in: absmax -> s = fp16(fp16(absmax / 7) * clip) -> codes, exactly as the stand-alone
+// quantiser; every CTA repeats this for its few rows, which costs less than a launch).  NT = threads of the CTA.
+template <int MT, bool F16, int NT>
+__device__ __forceinline__ void stage_token_rows(const GemvParams& p, unsigned char* smem_a, float* s_scale, float* s_red) {
   const int kbytes = p.K >> 1;
   const int nchunks = kbytes >> 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (p.x == nullptr) {
-    for (int i = threadIdx.x; i < MT * nchunks; i += kGemvThreads) {
+    for (int i = threadIdx.x; i < MT * nchunks; i += NT) {
       const int m = i / nchunks, c = i - m * nchunks;
       uint4 v = make_uint4(0, 0, 0, 0);
       if (m < p.M) v = *reinterpret_cast<const uint4*>(p.A + (size_t)m * kbytes + (size_t)c * 16);
@@ -68,7 +67,7 @@ gemv_i4_kernel(const GemvParams p) {
       if (m < p.M) {
         const uint4* xr = reinterpret_cast<const uint4*>(p.x + (size_t)m * p.ldx);
         __half2 mx = __float2half2_rn(0.0f);
-        for (int g = threadIdx.x; g < ngroups; g += kGemvThreads) {
+        for (int g = threadIdx.x; g < ngroups; g += NT) {
           const uint4 v = __ldg(xr + g);
           const __half2* h = reinterpret_cast<const __half2*>(&v);
           mx = __hmax2(mx, __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3]))));
@@ -79,7 +78,7 @@ gemv_i4_kernel(const GemvParams p) {
         for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
         if (lane == 0) s_red[warp] = a;
         __syncthreads();
-        a = (lane < kGemvThreads / 32) ? s_red[lane] : 0.0f;
+        a = (lane < NT / 32) ? s_red[lane] : 0.0f;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, o));
         __syncthreads();
@@ -88,17 +87,32 @@ gemv_i4_kernel(const GemvParams p) {
         const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
         const bool noclamp = clamp_free(s, p.clip);
         uint32_t* dst = reinterpret_cast<uint32_t*>(smem_a + (size_t)m * kbytes);
-        for (int g = threadIdx.x; g < ngroups; g += kGemvThreads) {
+        for (int g = threadIdx.x; g < ngroups; g += NT) {
           const uint4 v = __ldg(xr + g);
           dst[g] = quant8_words(v.x, v.y, v.z, v.w, s, rcp, noclamp);
         }
       } else {
         uint32_t* dst = reinterpret_cast<uint32_t*>(smem_a + (size_t)m * kbytes);
-        for (int g = threadIdx.x; g < ngroups; g += kGemvThreads) dst[g] = 0u;
+        for (int g = threadIdx.x; g < ngroups; g += NT) dst[g] = 0u;
       }
       if (threadIdx.x == 0) s_scale[m] = s;
     }
   }
+}
+
+// MT: token rows held per warp (M rounded up), ROWS: output channels a warp works on at a time (two share the
+// widening of the token rows; one gives twice as many warps when there are few output channels).
+template <int MT, int ROWS, bool F16>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_i4_kernel(const GemvParams p) {
+  constexpr int kGemvRows = ROWS;
+  extern __shared__ __align__(16) unsigned char smem_a[];      // MT x K/2 packed token rows (zero rows beyond M)
+  __shared__ float s_red[kGemvThreads / 32];
+  __shared__ float s_scale[MT];                                // per-token scales of the token rows
+  const int kbytes = p.K >> 1;
+  const int nchunks = kbytes >> 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  stage_token_rows<MT, F16, kGemvThreads>(p, smem_a, s_scale, s_red);
   __syncthreads();
 
   // The work of a warp is the flat sequence (channel pair, k step); the weight chunks of step t + 1 are requested
