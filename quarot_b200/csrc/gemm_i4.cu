@@ -382,6 +382,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   }
 
   // ---------------------------------------------------------------- teardown
+  drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -901,6 +902,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   }
 
   // ---------------------------------------------------------------- teardown
+  drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
   __syncwarp();
@@ -1312,6 +1314,7 @@ gemm_i4_2sm_ts_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_cons
   }
 
   // ---------------------------------------------------------------- teardown
+  drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
   __syncwarp();

@@ -375,6 +375,7 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
     }
   }
 
+  drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
   if (threadIdx.x == 0) stamp(1, 7, 1);

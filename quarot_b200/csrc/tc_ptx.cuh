@@ -47,6 +47,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// After a wait has timed out every role leaves its loop while TMA copies and MMAs that were already issued may still
+// be in flight towards this CTA's shared and tensor memory.  Before the CTA tears down (frees tensor memory, exits)
+// it therefore idles for a bounded time (about a millisecond of SM clock, far longer than any such operation takes).
+// In a healthy run the flag is clear and this costs one shared-memory read.
+__device__ __forceinline__ void drain_after_abort(volatile int* abort_flag) {
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {}
+  }
+}
+
 // Non-suspending poll (mbarrier.test_wait): used to measure how much of a wait is wake-up latency.
 __device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
