@@ -1457,14 +1457,21 @@ static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clus
 
 // Number of k splits the decode path would use for (M, N, K) and the scratch bytes that needs
 // (arrival counters, padded to 256 bytes, followed by the int32 partial tiles).
-static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t* counter_bytes = nullptr) {
+//  The rule: split only when the tiles alone leave SMs idle, as many ways as whole copies of the tile set fit on the
+//  SMs.  With a caller-provided workspace (measured = true) the rule is switched off where it was measured to lose:
+//  for more than 32 token rows the partial-tile epilogue (32 KB per item, re-read by the last arriver) costs more
+//  than the idle SMs (7B decode layer at M = 64: 147 us with splits, 134 us without).  Splitting further, so that
+//  the persistent CTAs take several (tile, split) items each, was measured too and loses badly (M = 32: 113 -> 235 us).
+static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t* counter_bytes = nullptr, bool measured = false) {
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   const int tiles = (int)((N + kBM - 1) / kBM) * (int)((M + bn - 1) / bn);
   const int num_kb = (int)((K + 127) / 128);
-  int splits = num_sms() / (tiles > 0 ? tiles : 1);
+  const int sms = num_sms();
+  int splits = sms / (tiles > 0 ? tiles : 1);
   if (splits > 8) splits = 8;
   if (splits > num_kb / 4) splits = num_kb / 4;
   if (splits < 1) splits = 1;
+  if (measured && M > 32) splits = 1;
   if (bytes) *bytes = splits > 1 ? (((size_t)tiles * 4 + 255) & ~(size_t)255) + (size_t)tiles * splits * bn * kBM * 4 : 0;
   if (counter_bytes) *counter_bytes = ((size_t)tiles * 4 + 255) & ~(size_t)255;
   return splits;
@@ -1582,7 +1589,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   if (ws && tuning("gemm_splitk", 1) != 0) {
     size_t need = 0, compact_counters = 0;
-    int splits = decode_splits(M, N, K, &need, &compact_counters);
+    int splits = decode_splits(M, N, K, &need, &compact_counters, !compact_ws);
     if (!compact_ws) {   // fixed counter region in front of the partial tiles
       if (compact_counters > kWsCounterRegion) splits = 1;
       need = need - compact_counters + kWsCounterRegion;
@@ -1648,7 +1655,7 @@ static size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0 || M > qr::tuning("gemm_swap_max_m", 64)) return 0;
   size_t bytes = 0, compact_counters = 0;
-  if (qr::decode_splits(M, N, K, &bytes, &compact_counters) <= 1 || compact_counters > qr::kWsCounterRegion) return 0;
+  if (qr::decode_splits(M, N, K, &bytes, &compact_counters, true) <= 1 || compact_counters > qr::kWsCounterRegion) return 0;
   return bytes - compact_counters + qr::kWsCounterRegion;
 }
 
