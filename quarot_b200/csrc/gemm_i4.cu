@@ -423,12 +423,13 @@ struct SmemLayout2 {
   static constexpr int kNumBars = 2 * PST + 2 * IST + 4;
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
-  static constexpr int kTotal = kAbortOff + 16;   // abort flag, issuer turn, scratch word, loads issued
+  static constexpr int kTotal = kAbortOff + 16;   // abort flag, issuer turn, scratch word
   static constexpr int kDynamic = kTotal + 1024;
 };
 
-constexpr int kWidenGroups2 = 3;                                  // widen groups of four warps, taking k-blocks round-robin
-constexpr int kWidenWarps2 = 4 * kWidenGroups2;
+constexpr int kWidenGroups2 = 4;                                  // widen groups of three warps; group g owns staging slot g
+constexpr int kWidenWarpsPerGroup2 = 3;
+constexpr int kWidenWarps2 = kWidenWarpsPerGroup2 * kWidenGroups2;
 // Warp roles.  A warp is served by the warp scheduler (id modulo 4) it was born on, and a scheduler shares its
 // issue slots evenly among its ready warps.  The two MMA issuers and the TMA producer are single threads whose
 // instruction latency is the critical path of the main loop, so scheduler 1 carries only them (warps 1, 5, 9),
@@ -439,6 +440,7 @@ constexpr int kIssuerBWarp = 5;
 constexpr int kProducerWarp2 = 9;
 constexpr int kThreads2 = 32 * 20;
 static_assert(kWidenWarps2 == 12, "widen_index2 enumerates twelve widen warps");
+static_assert(kWidenGroups2 == 4, "group g owns staging slot g and int8 slot g: four of each");
 __device__ __forceinline__ bool is_epilogue_warp2(int w) { return (w >= 2 && w <= 4) || w == 13; }
 // 0 .. 11 for the widen warps (0, 6-8, 10-12, 14-16, 18, 19), -1 otherwise
 __device__ __forceinline__ int widen_index2(int w) {
@@ -472,8 +474,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
   volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
-  // number of k-blocks whose TMA loads this CTA's producer has issued
-  volatile uint32_t* issued = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 12);
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
   pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
   if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[7 * 64 + 0] = clock64();   // life-cycle stamps live in slot 7
@@ -484,12 +484,11 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   }
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), 4); }   // four warps of the owning group
-    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), 8); mbar_init(empty_i(s), 1); }      // 4 local + 4 remote warps
+    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarpsPerGroup2); }   // the warps of the owning group
+    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), 2 * kWidenWarpsPerGroup2); mbar_init(empty_i(s), 1); }      // local + remote warps of the group
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 2); mbar_init(acc_empty(a), 2 * kEpiWarps); }
     *abort_flag = 0;
     *turn = 0;
-    *reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 12) = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -530,10 +529,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
           tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * 2 * kBM + (int)rank * kBM);
           tma_load_2d(dst + kBM * kBKBytes, &tmQ, full_p(s), kb * kBKBytes, tq * kBN2 + (int)rank * (kBN2 / 2));
-          // No ordering with the barrier operations is needed: all that a reader relies on is that this thread has
-          // passed its empty_p wait for this slot, which precedes the store in program order, and a CTA's shared
-          // memory is a single copy.
-          *issued = it + 1;
         }
       }
     }
@@ -814,15 +809,15 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     if (lane == 0) bulk_wait_read_all();   // the staging block must outlive the TMA unit's reads of it
   } else if (widen_index2(warp) >= 0) {
     // ------------------------------------------------------------ widen int4 -> int8 (own rows)
-    // Groups of four warps take the k-blocks round-robin, so that a group has kWidenGroups2 MMA periods
+    // Groups of three warps take the k-blocks round-robin, so that a group has kWidenGroups2 MMA periods
     // per stage (its stores and the proxy fence take more than one).  Packed data is read into registers
     // before the int8 slot is waited for, which keeps the shared-memory read off the slot-reuse path.
-    const int wt = widen_index2(warp) * 32 + lane;
-    const int group = wt >> 7;                          // four warps per group
-    const int gt = wt & 127;                            // 0 .. 127 inside the group
+    const int wi = widen_index2(warp);
+    const int group = wi / kWidenWarpsPerGroup2;                               // three warps per group
+    const int gt = (wi % kWidenWarpsPerGroup2) * 32 + lane;                    // 0 .. 95 inside the group
     constexpr int kChunks = kRows2 * 4;                 // 1024 packed 16-byte chunks per stage
-    constexpr int kGThreads = 128;
-    constexpr int kPer = kChunks / kGThreads;           // 8 chunks per thread
+    constexpr int kGThreads = 32 * kWidenWarpsPerGroup2;
+    constexpr int kPer = (kChunks + kGThreads - 1) / kGThreads;   // 11 chunks per thread (the last round is partial)
     const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
     uint32_t it = 0;
     bool ok = true;
@@ -831,31 +826,18 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         if ((int)(it % kWidenGroups2) != group) continue;
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
-        // A group comes back to a staging slot only every third use of it (3 groups, 4 slots), and TMA loads may
-        // complete out of order: the load of the slot's PREVIOUS use (k-block it - 4, read by another group) may
-        // still be in flight when this group gets here, and a parity wait cannot tell "previous phase not finished"
-        // from "this phase finished" (seen on the GPU as a rare deadlock).  The producer therefore publishes how
-        // many loads it has issued; once the load of k-block `it` is issued (which needs the previous use
-        // consumed), the barrier is in this phase or has completed it, and the parity wait is unambiguous.
-        // (A plain volatile read is enough on this side: the barrier wait below is control-dependent on it.)
-        if (*issued <= it) {
-          const long long t0 = clock64();
-          bool got = false;
-          for (uint32_t spin = 1; !got; ++spin) {
-            got = (*issued > it);
-            if (!got && (spin & 255u) == 0u) {
-              if (*abort_flag) break;
-              if (clock64() - t0 > kWaitCycles) { *abort_flag = 1; atomicExch(p.status, 18); break; }
-            }
-          }
-          if (!got) { ok = false; break; }
-        }
+        // Group g is the only reader of staging slot g (four groups, four slots), so it sees every phase of that
+        // slot's barrier in turn and a parity wait is unambiguous even when TMA loads complete out of order.  (With
+        // three groups a group came back to a slot only every third use; a load of the previous use still in flight
+        // then looked like "this phase complete" and deadlocked the pipeline.)
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
         if (gt == 0) stamp(0, it, 4);
         const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
         uint4 w[kPer];
 #pragma unroll
-        for (int j = 0; j < kPer; ++j) w[j] = *reinterpret_cast<const uint4*>(pk + (gt + j * kGThreads) * 16);
+        for (int j = 0; j < kPer; ++j)
+          w[j] = (gt + j * kGThreads < kChunks) ? *reinterpret_cast<const uint4*>(pk + (gt + j * kGThreads) * 16)
+                                                : make_uint4(0, 0, 0, 0);
         // Hand the staging slot back to the TMA producer as soon as the packed data is in registers.  The
         // arrive must not overtake the loads, so it is made to depend on every loaded word: the words are
         // folded into one value that feeds a (practically never taken) predicated store.
@@ -879,6 +861,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
           const int c = gt + j * kGThreads;
+          if (c >= kChunks) break;
           const int row = c >> 2, cc = c & 3;
           uint4 lo, hi;
           lo.x = (w[j].x << 4) & 0xF0F0F0F0u; hi.x = w[j].x & 0xF0F0F0F0u;
