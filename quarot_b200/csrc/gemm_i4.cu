@@ -111,10 +111,14 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 
   constexpr uint32_t kTmemCols = (ACC * BN) < 32 ? 32 : (ACC * BN);
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
+  // The widen warps work as two groups that take alternate k-blocks when both rings have an even number of slots:
+  // a group then always meets the same slots (those of its parity), one phase after the other, so its parity
+  // waits stay unambiguous, and it has two MMA periods for the latency chain wait -> read -> store -> fence -> arrive.
+  constexpr int kGroups = (PST % 2 == 0 && IST % 2 == 0) ? 2 : 1;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps); }
-    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), kWidenWarps); mbar_init(empty_i(s), 1); }
+    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps / kGroups); }
+    for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), kWidenWarps / kGroups); mbar_init(empty_i(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 1); mbar_init(acc_empty(a), kEpiWarps); }
     *abort_flag = 0;
     fence_mbar_init();
@@ -343,13 +347,16 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     }
   } else {
     // ------------------------------------------------------------ widen int4 -> int8
-    const int wt = threadIdx.x - 32 * (2 + kEpiWarps);  // 0 .. 255
+    const int wt_all = threadIdx.x - 32 * (2 + kEpiWarps);  // 0 .. 255
     constexpr int kChunks = (kBM + BN) * 4;             // 16-byte packed chunks per stage
-    constexpr int kWThreads = 32 * kWidenWarps;
+    constexpr int kWThreads = 32 * kWidenWarps / kGroups;   // threads of one group
+    const int group = wt_all / kWThreads;
+    const int wt = wt_all - group * kWThreads;
     uint32_t it = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
       for (int kb = kb_begin(w); kb < kb_end(w); ++kb, ++it) {
+        if ((int)(it % kGroups) != group) continue;
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 5)) { ok = false; break; }
