@@ -53,14 +53,10 @@ const char* qr_last_error(void);
  * device.  No upstream counterpart (upstream never checks launches). */
 int qr_kernel_status(int* status_out);
 
-/* Tuning knobs for experiments: key is e.g. "gemm_bn", "gemm_pst", "gemm_ist".
- * Unknown keys return QR_EINVAL. No upstream counterpart. */
+/* Kernel-selection knobs, process-wide: "gemm_bn", "gemm_pst", "gemm_grid", "gemm_swap_max_m", "gemm_splitk",
+ * "gemm_2sm", "gemm_tma_out", "gemv_max_m", "pdl", "hadq_path", "hadq_tc".  Every setting computes the same
+ * results; the defaults are the measured best choices.  Unknown keys return QR_EINVAL.  No upstream counterpart. */
 int qr_set_tuning(const char* key, int value);
-
-/* Debugging aid: when non-null, the 2-CTA GEMM writes clock64 stamps of the first 64 k-blocks of its
- * first cluster into this device buffer (2 x 8 x 64 int64).  Pass NULL to switch it off.  No upstream
- * counterpart. */
-int qr_debug_set_trace(void* device_buffer);
 
 /* Self-test: the quantisers divide by the row scale with one multiplication by the rounded reciprocal.  This
  * runs every finite fp16 value against every finite non-zero fp16 scale on the current device and counts the

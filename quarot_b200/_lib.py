@@ -24,7 +24,6 @@ SIGNATURES = {
     "qr_last_error": (ctypes.c_char_p, []),
     "qr_kernel_status": (_int, [ctypes.POINTER(_int)]),
     "qr_set_tuning": (_int, [ctypes.c_char_p, _int]),
-    "qr_debug_set_trace": (_int, [_vp]),
     "qr_debug_division_check": (_int, [ctypes.POINTER(ctypes.c_uint64)]),
     "qr_hadamard_f16": (_int, [_vp, _vp, _i64, _i64, _vp, _int, _vp]),
     "qr_hadamard_f32": (_int, [_vp, _vp, _i64, _i64, _vp, _int, _vp]),

@@ -3,7 +3,6 @@
 
 #include <map>
 #include <mutex>
-#include <string>
 #include <string.h>
 
 namespace qr {
@@ -62,17 +61,8 @@ int num_sms() {
   return n;
 }
 
-static void* g_trace_ptr = nullptr;   // set through qr_debug_set_trace (debugging aid)
-void* debug_trace_ptr() { return g_trace_ptr; }
-
-static std::mutex g_tune_mu;
-static std::map<std::string, int> g_tune;
-
-int tuning(const char* key, int dflt) {
-  std::lock_guard<std::mutex> lk(g_tune_mu);
-  auto it = g_tune.find(key);
-  return it == g_tune.end() ? dflt : it->second;
-}
+// Tuning knobs: plain ints that qr_set_tuning overwrites; the launch path reads them without a lock or a lookup.
+Tuning g_tuning;
 
 }  // namespace qr
 
@@ -95,19 +85,19 @@ int qr_kernel_status(int* status_out) {
   return QR_OK;
 }
 
-int qr_debug_set_trace(void* device_buffer) {
-  qr::g_trace_ptr = device_buffer;
-  return QR_OK;
-}
-
 int qr_set_tuning(const char* key, int value) {
-  static const char* known[] = {"gemm_bn", "gemm_pst", "gemm_ist", "gemm_acc", "gemm_grid",
-                                "gemm_swap_max_m", "gemm_splitk", "gemm_2sm", "gemm_ts", "gemm_sync", "gemm_debug", "gemm_tma_out", "gemv_max_m", "pdl", "hadq_debug", "hadq_path", "hadq_tc", nullptr};
+  static const struct { const char* name; int qr::Tuning::*field; } known[] = {
+      {"gemm_bn", &qr::Tuning::gemm_bn},           {"gemm_pst", &qr::Tuning::gemm_pst},
+      {"gemm_grid", &qr::Tuning::gemm_grid},       {"gemm_swap_max_m", &qr::Tuning::gemm_swap_max_m},
+      {"gemm_splitk", &qr::Tuning::gemm_splitk},   {"gemm_2sm", &qr::Tuning::gemm_2sm},
+      {"gemm_tma_out", &qr::Tuning::gemm_tma_out}, {"gemv_max_m", &qr::Tuning::gemv_max_m},
+      {"pdl", &qr::Tuning::pdl},                   {"hadq_path", &qr::Tuning::hadq_path},
+      {"hadq_tc", &qr::Tuning::hadq_tc},
+  };
   if (!key) return qr::fail(QR_EINVAL, "qr_set_tuning: null key");
-  for (int i = 0; known[i]; ++i) {
-    if (strcmp(known[i], key) == 0) {
-      std::lock_guard<std::mutex> lk(qr::g_tune_mu);
-      qr::g_tune[key] = value;
+  for (const auto& k : known) {
+    if (strcmp(k.name, key) == 0) {
+      qr::g_tuning.*(k.field) = value;
       return QR_OK;
     }
   }

@@ -16,8 +16,22 @@ int fail(int code, const char* fmt, ...);
 int cuda_fail(cudaError_t e, const char* what);
 int* kernel_status_ptr();        // device address of the per-device status word (lazy, no allocation)
 int num_sms();
-int tuning(const char* key, int dflt);
-void* debug_trace_ptr();   // device buffer for clock64 time lines of a kernel, or null (debugging aid)
+
+// Kernel-selection knobs (qr_set_tuning); the defaults are the measured best choices.
+struct Tuning {
+  int gemm_bn = 256;          // N tile of the 1-CTA GEMM (256, 128 or 64)
+  int gemm_pst = 4;           // packed staging slots of the 1-CTA GEMM at BN = 256 (4 or 3)
+  int gemm_grid = 0;          // cap on the number of persistent CTAs / clusters (0 = one per SM / SM pair)
+  int gemm_swap_max_m = 64;   // token rows up to which the weights take the MMA rows (decode)
+  int gemm_splitk = 1;        // decode: split the K loop over several CTAs when a workspace is given
+  int gemm_2sm = 1;           // prefill: 2-CTA kernel (cta_group::2) instead of the 1-CTA kernel
+  int gemm_tma_out = 1;       // 2-CTA kernel: tiled TMA stores of the output where alignment allows
+  int gemv_max_m = 8;         // token rows up to which the weight-streaming CUDA-core kernel is used
+  int pdl = 0;                // launch the kernels with programmatic stream serialization
+  int hadq_path = 0;          // 1 = always the generic Hadamard kernel (A/B checks)
+  int hadq_tc = 1;            // tensor-core kernel for n = 64 K Kronecker shapes
+};
+extern Tuning g_tuning;
 
 #define QR_CUDA(expr)                                            \
   do {                                                           \

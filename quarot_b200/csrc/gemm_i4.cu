@@ -52,13 +52,9 @@ struct GemmParams {
   const __half* sP;      // per-row scale of operand P (fp16) or null (MODE_I32)
   const __half* sQ;
   const __half* bias;    // per output channel or null
-  int sync_mode;         // 2-CTA kernel: bit 0 = plain remote arrives, bit 1 = plain (CTA-scope) waits in the MMA thread,
-                         // bit 2 = one commit delivered to both CTAs instead of one commit per CTA
   int splits;            // 1-CTA kernel: k splits per tile (1 = none); > 1 needs the scratch buffers below
   int32_t* ws_partial;   // [tiles][splits][BN][128] int32 partial tiles
   int* ws_counter;       // [tiles] arrival counters, zero before and after every launch
-  long long* trace;      // optional device buffer [2 CTAs][8 slots][64] for clock64 stamps of cluster 0, or null
-  int debug;             // timing experiments only (results are wrong when non-zero)
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int swiglu;            // 2-CTA kernel, fp16 mode: columns [0,128) / [128,256) of a tile are gate / up channels; out = silu(gate) * up
   int n_outs;            // 2-CTA kernel: number of output matrices that receive the result (1, or one per GPU of a column split)
@@ -483,7 +479,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
   constexpr uint32_t kTmemCols = ACC * kBN2;  // 512
   pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[7 * 64 + 0] = clock64();   // life-cycle stamps live in slot 7
   if (threadIdx.x == 32) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmP) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&tmQ) : "memory");
@@ -508,16 +503,10 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // optional timeline (debugging aid): cluster 0 records clock64 stamps of its first 64 k-blocks
-  long long* trace = (p.trace && (blockIdx.x >> 1) == 0) ? p.trace + (size_t)(blockIdx.x & 1) * 8 * 64 : nullptr;
-  auto stamp = [&](int lane_id, uint32_t it_, int slot) {
-    if (trace && lane_id == 0 && it_ < 64) trace[(size_t)slot * 64 + it_] = clock64();
-  };
   const int num_tiles = p.tilesP * p.tilesQ;     // pair tiles
   const int num_kb = (p.K + 127) >> 7;
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
-  if (threadIdx.x == 0) stamp(0, 1, 7);
 
   if (warp == kProducerWarp2) {
     // ------------------------------------------------------------ TMA producer (own rows only)
@@ -531,7 +520,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           const int s = it % PST;
           const uint32_t ph = (it / PST) & 1;
           if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
-          stamp(0, it, 0);
           mbar_expect_tx(full_p(s), L::kPkStage);
           const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
           tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * 2 * kBM + (int)rank * kBM);
@@ -550,7 +538,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     if (leader && lane == 0) {
       const int me = (warp == kIssuerAWarp) ? 0 : 1;
       constexpr uint32_t idesc = make_idesc_i8(2 * kBM, kBN2);
-      const uint32_t peer_empty_i0 = mapa_cluster(empty_i(0), 1);
       const uint32_t peer_acc_full0 = mapa_cluster(acc_full(0), 1);
       uint32_t it = 0, tl = 0;
       bool ok = true;
@@ -594,24 +581,12 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           umma_i8_2sm_w<1>(d_tmem, a_lo + 6, b_lo + 6, kDescHiKmajorSw128, idesc);
           tc_fence_before();
           *turn = it + 1;
-          stamp(0, it, 2);
-          if (p.sync_mode & 4) {
-            umma_commit_2sm_mc(empty_i(s), 3);
-          } else {
-            umma_commit_2sm(empty_i(s));
-            umma_commit_2sm(peer_empty_i0 + 8u * s);
-          }
-          stamp(0, it, 3);
+          umma_commit_2sm_mc(empty_i(s), 3);   // one completion signal, delivered to the same barrier in both CTAs
         }
         if (!ok) break;
         // accumulator ready: acc_full needs both issuers (a commit only tracks the MMAs of its own thread)
         if (mine_in_tile) {
-          if (p.sync_mode & 4) {
-            umma_commit_2sm_mc(acc_full(a), 3);
-          } else {
-            umma_commit_2sm(acc_full(a));
-            umma_commit_2sm(peer_acc_full0 + 8u * a);
-          }
+          umma_commit_2sm_mc(acc_full(a), 3);
         } else {
           mbar_arrive(acc_full(a));
           mbar_arrive_cluster_relaxed(peer_acc_full0 + 8u * a);
@@ -657,7 +632,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
       }
       if (!mbar_wait(acc_full(a), pha, abort_flag, p.status, 14)) { ok = false; break; }
       tc_fence_after();
-      if (q4 == 0) stamp(lane, 8 + 2 * tl, 7);
       const int prow = tp * 2 * kBM + (int)rank * kBM + prow_in_tile;
       const bool prow_ok = prow < p.rowsP;
       float sp = 0.0f;
@@ -666,10 +640,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         tc_fence_before();
         __syncwarp();
         if (lane == 0) {
-          if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_acc_empty0 + 8u * a);
-          else mbar_arrive_cluster(leader_acc_empty0 + 8u * a);
+          mbar_arrive_cluster_relaxed(leader_acc_empty0 + 8u * a);
         }
-        if (q4 == 0) stamp(lane, 9 + 2 * tl, 7);
       };
       if (MODE == MODE_F16 && p.swiglu) {
         // Gate and up projections computed as ONE GEMM over row-interleaved weights: columns [0,128) of the tile are
@@ -811,7 +783,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           }
         }
       }
-      if (q4 == 0) stamp(lane, 32 + tl, 7);
     }
     if (lane == 0) bulk_wait_read_all();   // the staging block must outlive the TMA unit's reads of it
   } else if (widen_index2(warp) >= 0) {
@@ -838,7 +809,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         // three groups a group came back to a slot only every third use; a load of the previous use still in flight
         // then looked like "this phase complete" and deadlocked the pipeline.)
         if (!mbar_wait(full_p(sp_), php, abort_flag, p.status, 15)) { ok = false; break; }
-        if (gt == 0) stamp(0, it, 4);
         const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage;
         uint4 w[kPer];
 #pragma unroll
@@ -863,7 +833,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
         if (!mbar_wait(empty_i(si), phi ^ 1, abort_flag, p.status, 16)) { ok = false; break; }
         tc_fence_after();
-        if (gt == 0) stamp(0, it, 5);
         unsigned char* i8 = smem_gen + L::kI8Off + si * L::kI8Stage;
 #pragma unroll
         for (int j = 0; j < kPer; ++j) {
@@ -883,10 +852,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          if (p.sync_mode & 1) mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * si);
-          else mbar_arrive_cluster(leader_full_i0 + 8u * si);
+          mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * si);
         }
-        if (gt == 0) stamp(0, it, 6);
       }
     }
   }
@@ -897,418 +864,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   __syncthreads();
   __syncwarp();
   cluster_sync_all();   // the peer may still read this CTA's shared memory or arrive on its barriers
-  if (threadIdx.x == 0) stamp(0, 63, 7);
-  if (warp == 1) {
-    __syncwarp();
-    tc_fence_after();
-    tmem_dealloc_2sm(tmem_base, kTmemCols);
-  }
-}
-
-// ------------------------------------------------------------------ 2-CTA kernel, A through tensor memory
-// Same pair tile (256 x 256) and barrier protocol as gemm_i4_2sm_kernel, but operand A never
-// touches shared memory after its packed tile has been read: four warps (one accumulator-lane
-// quarter each) widen one A row per thread in registers and write it with tcgen05.st into a ring
-// of 64-column slots in tensor memory; the MMA takes A from there
-// (tcgen05.mma [d], [a_tmem], b_desc).  Only the half weight tile is widened into shared memory.
-// Per 128-deep k-block and CTA the shared-memory pipe then moves 512 wavefronts (TMA fill 128, packed
-// reads 128, int8 B stores 128, tensor-core B reads 128) instead of 768.  Tensor memory holds the
-// accumulator (256 columns) and the A ring (256 columns), so there is a single accumulator
-// buffer: the next tile's MMAs start when the epilogue has finished reading it, while the TMA
-// and widen warps already run ahead.
-// A pipeline stage covers kTSSub = 2 k sub-blocks of 128 (one barrier round trip and one commit per
-// 256 K values).  The packed A tile is loaded with the 128-byte TMA swizzle so that the per-row
-// 16-byte reads of the A warps are bank-conflict free.
-constexpr int kTSSub = 2;            // 128-deep k sub-blocks per pipeline stage (one barrier round trip per stage)
-constexpr int kStagesTS = 4;         // operand stages: B in shared memory, A in a tensor-memory ring
-constexpr int kThreadsTS = 32 * (2 + kEpiWarps + 8 + 8);   // producer, MMA, 4 epilogue, 8 A-widen, 8 B-widen warps
-
-template <int PST>
-struct SmemLayoutTS {
-  static constexpr int kBSub = (kBN2 / 2) * 128;               // int8 half weight tile of one k sub-block
-  static constexpr int kBStage = kTSSub * kBSub;
-  static constexpr int kPkRow = kTSSub * kBKBytes;             // packed bytes per row per stage
-  static constexpr int kPkStage = kRows2 * kPkRow;             // packed A rows + packed B rows
-  static constexpr int kBOff = 0;
-  static constexpr int kPkOff = kStagesTS * kBStage;
-  static constexpr int kEpiOff = kPkOff + PST * kPkStage;     // 4 KB of output staging per epilogue warp
-  static constexpr int kBarOff = kEpiOff + kEpiWarps * 4096;
-  static constexpr int kNumBars = 2 * PST + 2 * kStagesTS + 2;
-  static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
-  static constexpr int kAbortOff = kTmemSlotOff + 8;
-  static constexpr int kTotal = kAbortOff + 8;
-  static constexpr int kDynamic = kTotal + 1024;
-};
-
-template <int PST, int MODE>
-__global__ void __launch_bounds__(kThreadsTS, 1)
-gemm_i4_2sm_ts_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
-  using L = SmemLayoutTS<PST>;
-  constexpr int ST = kStagesTS;
-  static_assert(kBN2 + ST * 32 * kTSSub <= 512, "accumulator + A ring exceed tensor memory");
-  extern __shared__ unsigned char smem_dyn[];
-  const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
-  unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
-
-  const int warp = threadIdx.x >> 5;
-  const int lane = threadIdx.x & 31;
-  const uint32_t rank = cluster_ctarank();
-  const bool leader = (rank == 0);
-
-  const uint32_t bar_base = smem_base + L::kBarOff;
-  auto full_p = [&](int s) { return bar_base + 8u * s; };
-  auto empty_p = [&](int s) { return bar_base + 8u * (PST + s); };
-  auto full_i = [&](int s) { return bar_base + 8u * (2 * PST + s); };
-  auto empty_i = [&](int s) { return bar_base + 8u * (2 * PST + ST + s); };
-  const uint32_t acc_full = bar_base + 8u * (2 * PST + 2 * ST);
-  const uint32_t acc_empty = bar_base + 8u * (2 * PST + 2 * ST + 1);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
-  constexpr uint32_t kTmemCols = 512;
-  constexpr uint32_t kAringCol = kBN2;   // A ring starts after the 256 accumulator columns
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarps); }
-    for (int s = 0; s < ST; ++s) { mbar_init(full_i(s), (p.debug & 64) ? kWidenWarps : 2 * kWidenWarps); mbar_init(empty_i(s), 1); }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 2 * kEpiWarps);
-    *abort_flag = 0;
-    fence_mbar_init();
-  }
-  if (warp == 1) {
-    tmem_alloc_2sm(smem_base + L::kTmemSlotOff, kTmemCols);
-    tmem_relinquish_2sm();
-  }
-  tc_fence_before();
-  __syncthreads();
-  cluster_sync_all();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-
-  const bool spin = (p.debug & 32) != 0;
-  auto wait = [&](uint32_t bar, uint32_t parity, int code) {
-    return spin ? mbar_wait_spin(bar, parity, abort_flag, p.status, code) : mbar_wait(bar, parity, abort_flag, p.status, code);
-  };
-  const int num_tiles = p.tilesP * p.tilesQ;
-  const int num_kb = (p.K + 128 * kTSSub - 1) / (128 * kTSSub);   // pipeline stages per tile
-  const int cluster_id = blockIdx.x >> 1;
-  const int num_clusters = gridDim.x >> 1;
-
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-        const int tp = tile % p.tilesP, tq = tile / p.tilesP;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % PST;
-          const uint32_t ph = (it / PST) & 1;
-          if (!wait(empty_p(s), ph ^ 1, 21)) { ok = false; break; }
-          if (p.debug & 2) { mbar_arrive(full_p(s)); continue; }   // timing experiment: no loads
-          mbar_expect_tx(full_p(s), L::kPkStage);
-          const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
-          tma_load_2d(dst, &tmP, full_p(s), kb * L::kPkRow, tp * 2 * kBM + (int)rank * kBM);
-          tma_load_2d(dst + kBM * L::kPkRow, &tmQ, full_p(s), kb * L::kPkRow, tq * kBN2 + (int)rank * (kBN2 / 2));
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer (leader CTA only)
-    if (leader && lane == 0) {
-      constexpr uint32_t idesc = make_idesc_i8(2 * kBM, kBN2);
-      const uint32_t peer_empty_i0 = mapa_cluster(empty_i(0), 1);
-      const uint32_t peer_acc_full = mapa_cluster(acc_full, 1);
-      uint32_t it = 0, tl = 0;
-      bool ok = true;
-      for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
-        if (!wait(acc_empty, (tl & 1) ^ 1, 22)) { ok = false; break; }
-        tc_fence_after();
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % ST;
-          const uint32_t ph = (it / ST) & 1;
-          if (!wait(full_i(s), ph, 23)) { ok = false; break; }
-          if (!(p.debug & 1024)) tc_fence_after();
-          const uint32_t a_tmem = tmem_base + kAringCol + s * (32 * kTSSub);
-          if (!(p.debug & 4)) {
-#pragma unroll
-            for (int sub = 0; sub < kTSSub; ++sub) {
-              const uint64_t db = make_kmajor_sw128_desc(smem_base + L::kBOff + s * L::kBStage + sub * L::kBSub);
-#pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4)
-                umma_i8_2sm_ts(tmem_base, a_tmem + 32 * sub + 8 * k4, db + 2 * k4, idesc, (kb | sub | k4) != 0 ? 1u : 0u);
-            }
-          }
-          if (p.debug & 2048) {     // timing experiment: plain arrives instead of a commit
-            mbar_arrive(empty_i(s));
-            mbar_arrive_cluster_relaxed(peer_empty_i0 + 8u * s);
-          } else if (p.sync_mode & 4) {
-            umma_commit_2sm_mc(empty_i(s), 3);
-          } else {
-            umma_commit_2sm(empty_i(s));
-            umma_commit_2sm(peer_empty_i0 + 8u * s);
-          }
-        }
-        if (ok) {
-          if (p.sync_mode & 4) {
-            umma_commit_2sm_mc(acc_full, 3);
-          } else {
-            umma_commit_2sm(acc_full);
-            umma_commit_2sm(peer_acc_full);
-          }
-        }
-      }
-    }
-  } else if (warp < 2 + kEpiWarps) {
-    // ------------------------------------------------------------ epilogue (own 128 accumulator rows)
-    const int q4 = warp & 3;
-    const int prow_in_tile = q4 * 32 + lane;
-    const uint32_t leader_acc_empty = mapa_cluster(acc_empty, 0);
-    uint32_t tl = 0;
-    bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters, ++tl) {
-      const int tp = tile % p.tilesP, tq = tile / p.tilesP;
-      if (!wait(acc_full, tl & 1, 24)) { ok = false; break; }
-      tc_fence_after();
-      const int prow = tp * 2 * kBM + (int)rank * kBM + prow_in_tile;
-      const bool prow_ok = prow < p.rowsP;
-      float sp = 0.0f;
-      if (MODE == MODE_F16 && prow_ok) sp = __half2float(p.sP[prow]);
-      if (p.debug & 16) {   // timing experiment: no epilogue work at all
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster_relaxed(leader_acc_empty);
-        continue;
-      }
-      const bool staged = p.vec_ok && (tq * kBN2 + kBN2 <= p.rowsQ) && !(p.debug & 8);
-      if (staged) {
-        // Fast path: 128-byte row segments are assembled in shared memory (swizzled, conflict free) and
-        // written with fully coalesced 16-byte stores, four complete 128-byte lines per instruction.
-        unsigned char* stg = smem_gen + L::kEpiOff + (warp - 2) * 4096;
-        const int row0 = tp * 2 * kBM + (int)rank * kBM + q4 * 32;          // first output row of this warp
-        constexpr int kGroupCols = (MODE == MODE_F16) ? 64 : 32;             // columns per 128-byte segment
-#pragma unroll 1
-        for (int c0 = 0; c0 < kBN2; c0 += kGroupCols) {
-          const int qcol0 = tq * kBN2 + c0;
-#pragma unroll
-          for (int hseg = 0; hseg < kGroupCols / 32; ++hseg) {
-            uint32_t r[32];
-            tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(c0 + 32 * hseg), r);
-            if (c0 + kGroupCols >= kBN2 && hseg == kGroupCols / 32 - 1) {
-              tc_fence_before();
-              __syncwarp();
-              if (lane == 0) mbar_arrive_cluster_relaxed(leader_acc_empty);
-            }
-            if (MODE == MODE_F16) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __half2* h = reinterpret_cast<__half2*>(&pk);
-                const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + 32 * hseg + j));
-                const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 sc = __half22float2(sqh[e]);
-                  h[e] = __floats2half2_rn((float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x),
-                                           (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y));
-                }
-                if (p.bias) {
-                  const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + 32 * hseg + j));
-                  const __half2* bh = reinterpret_cast<const __half2*>(&bb);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
-                }
-                const int ch = 4 * hseg + (j >> 3);
-                *reinterpret_cast<uint4*>(stg + lane * 128 + ((ch ^ (lane & 7)) << 4)) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                const int ch = j >> 2;
-                *reinterpret_cast<int4*>(stg + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
-                    make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8, (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
-              }
-            }
-          }
-          __syncwarp();
-          unsigned char* obase = reinterpret_cast<unsigned char*>(p.out) + (int64_t)qcol0 * (MODE == MODE_F16 ? 2 : 4);
-          const int64_t row_bytes = p.ldo * (MODE == MODE_F16 ? 2 : 4);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const int rr = (lane >> 3) + 4 * j, ch = lane & 7;
-            const uint4 v = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((ch ^ (rr & 7)) << 4));
-            if (row0 + rr < p.rowsP)
-              *reinterpret_cast<uint4*>(obase + (int64_t)(row0 + rr) * row_bytes + ch * 16) = v;
-          }
-          __syncwarp();
-        }
-        continue;
-      }
-#pragma unroll 1
-      for (int c0 = 0; c0 < kBN2; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)c0, r);
-        if (c0 + 32 >= kBN2) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster_relaxed(leader_acc_empty);
-        }
-        const int qcol0 = tq * kBN2 + c0;
-        if (prow_ok && !(p.debug & 8)) {
-          if (MODE == MODE_I32) {
-            int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-            if (qcol0 + 32 <= p.rowsQ && p.vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
-                                                            (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (qcol0 + j < p.rowsQ) o[j] = (int32_t)r[j] >> 8;
-            }
-          } else {
-            __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-            if ((qcol0 + 32 <= p.rowsQ) && p.vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __half2* h = reinterpret_cast<__half2*>(&pk);
-                const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + j));
-                const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 sc = __half22float2(sqh[e]);
-                  h[e] = __floats2half2_rn((float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x),
-                                           (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y));
-                }
-                if (p.bias) {
-                  const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + j));
-                  const __half2* bh = reinterpret_cast<const __half2*>(&bb);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
-                }
-                *reinterpret_cast<uint4*>(o + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (qcol0 + j < p.rowsQ) {
-                  const float sc = __half2float(p.sQ[qcol0 + j]);
-                  __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sp * sc));
-                  if (p.bias) v = __hadd(v, p.bias[qcol0 + j]);
-                  o[j] = v;
-                }
-              }
-            }
-          }
-        }
-      }
-    }
-  } else if (warp < 2 + kEpiWarps + 8) {
-    // ------------------------------------------------------------ widen A: one row per thread, into tensor memory
-    // eight warps: two per TMEM lane quarter, taking alternate k-blocks
-    const int group = (warp - (2 + kEpiWarps)) >> 2;
-    const int q4 = warp & 3;                      // TMEM lane quarter this warp may write
-    const int row = q4 * 32 + lane;
-    const int sw = row & 7;                       // 128-byte TMA swizzle: 16-byte chunk index XOR row % 8
-    const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
-    uint32_t it = 0;
-    bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        if ((int)(it & 1u) != group) continue;
-        const int sp_ = it % PST, s = it % ST;
-        const uint32_t php = (it / PST) & 1, phi = (it / ST) & 1;
-        if (!wait(full_p(sp_), php, 25)) { ok = false; break; }
-        const unsigned char* prow_ptr = smem_gen + L::kPkOff + sp_ * L::kPkStage + row * L::kPkRow;
-        uint4 w[4 * kTSSub];
-#pragma unroll
-        for (int c = 0; c < 4 * kTSSub; ++c) w[c] = *reinterpret_cast<const uint4*>(prow_ptr + ((c ^ sw) << 4));
-        if (!((p.debug & 64) && !leader) && !wait(empty_i(s), phi ^ 1, 26)) { ok = false; break; }
-        tc_fence_after();
-#pragma unroll
-        for (int sub = 0; sub < kTSSub; ++sub) {
-          uint32_t v[32];
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const uint4 ww = w[4 * sub + c];
-            v[8 * c + 0] = (ww.x << 4) & 0xF0F0F0F0u; v[8 * c + 4] = ww.x & 0xF0F0F0F0u;
-            v[8 * c + 1] = (ww.y << 4) & 0xF0F0F0F0u; v[8 * c + 5] = ww.y & 0xF0F0F0F0u;
-            v[8 * c + 2] = (ww.z << 4) & 0xF0F0F0F0u; v[8 * c + 6] = ww.z & 0xF0F0F0F0u;
-            v[8 * c + 3] = (ww.w << 4) & 0xF0F0F0F0u; v[8 * c + 7] = ww.w & 0xF0F0F0F0u;
-          }
-          if (!(p.debug & 1))
-            tmem_st32(tmem_base + ((uint32_t)(q4 * 32) << 16) + kAringCol + (uint32_t)(s * 32 * kTSSub + 32 * sub), v);
-        }
-        if (!(p.debug & 512)) tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if (leader && (p.debug & 128)) mbar_arrive(full_i(s));
-          else if (!((p.debug & 64) && !leader)) mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * s);
-          mbar_arrive(empty_p(sp_));
-        }
-      }
-    }
-  } else {
-    // ------------------------------------------------------------ widen B: own half of the weight tile, into shared memory
-    // eight warps in two groups of four, taking alternate k-blocks
-    const int wb = warp - (2 + kEpiWarps + 8);               // 0 .. 7
-    const int group = wb >> 2;
-    const int wt = (wb & 3) * 32 + lane;                     // 0 .. 127 inside the group
-    // 512 packed 16-byte chunks per stage, four per thread
-    const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
-    uint32_t it = 0;
-    bool ok = true;
-    for (int tile = cluster_id; tile < num_tiles && ok; tile += num_clusters) {
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        if ((int)(it & 1u) != group) continue;
-        const int sp_ = it % PST, s = it % ST;
-        const uint32_t php = (it / PST) & 1, phi = (it / ST) & 1;
-        if (!wait(full_p(sp_), php, 27)) { ok = false; break; }
-        const unsigned char* pk = smem_gen + L::kPkOff + sp_ * L::kPkStage + kBM * L::kPkRow;
-        constexpr int kPerB = 4 * kTSSub;                    // packed 16-byte chunks per thread per stage
-        constexpr int kCpr = 4 * kTSSub;                     // packed chunks per row
-        uint4 w[kPerB];
-#pragma unroll
-        for (int j = 0; j < kPerB; ++j) w[j] = *reinterpret_cast<const uint4*>(pk + (wt + j * 128) * 16);
-        if (!((p.debug & 64) && !leader) && !wait(empty_i(s), phi ^ 1, 28)) { ok = false; break; }
-        tc_fence_after();
-        unsigned char* i8s = smem_gen + L::kBOff + s * L::kBStage;
-#pragma unroll
-        for (int j = 0; j < kPerB; ++j) {
-          if (p.debug & 1) break;
-          const int c = wt + j * 128;
-          const int row = c / kCpr, ccs = c % kCpr;          // row of the half tile, packed chunk within the stage row
-          const int cc = ccs & 3;
-          unsigned char* i8 = i8s + (ccs >> 2) * L::kBSub;   // k sub-block this chunk belongs to
-          uint4 lo, hi;
-          lo.x = (w[j].x << 4) & 0xF0F0F0F0u; hi.x = w[j].x & 0xF0F0F0F0u;
-          lo.y = (w[j].y << 4) & 0xF0F0F0F0u; hi.y = w[j].y & 0xF0F0F0F0u;
-          lo.z = (w[j].z << 4) & 0xF0F0F0F0u; hi.z = w[j].z & 0xF0F0F0F0u;
-          lo.w = (w[j].w << 4) & 0xF0F0F0F0u; hi.w = w[j].w & 0xF0F0F0F0u;
-          unsigned char* drow = i8 + row * 128;
-          const int swz = row & 7;
-          *reinterpret_cast<uint4*>(drow + (((2 * cc) ^ swz) << 4)) = lo;
-          *reinterpret_cast<uint4*>(drow + (((2 * cc + 1) ^ swz) << 4)) = hi;
-        }
-        if (!(p.debug & 256)) fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (leader && (p.debug & 128)) mbar_arrive(full_i(s));
-          else if (!((p.debug & 64) && !leader)) mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * s);
-          mbar_arrive(empty_p(sp_));
-        }
-      }
-    }
-  }
-
-  // ---------------------------------------------------------------- teardown
-  drain_after_abort(abort_flag);
-  tc_fence_before();
-  __syncthreads();
-  __syncwarp();
-  cluster_sync_all();
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -1336,7 +891,7 @@ static EncodeTiledFn get_encode_fn() {
 
 // Tensor map over a packed int4 matrix [rows, kbytes] (uint8), box = [64 bytes, box_rows], no swizzle.
 static int make_packed_map(CUtensorMap* map, const void* base, int64_t rows, int64_t kbytes, int box_rows,
-                           int box_bytes = kBKBytes, bool swizzle = false) {
+                           int box_bytes = kBKBytes) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(QR_ENOTREADY, "cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
@@ -1344,7 +899,7 @@ static int make_packed_map(CUtensorMap* map, const void* base, int64_t rows, int
   cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle ? (box_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B) : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(QR_EINVAL, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -1383,21 +938,13 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
   int grid = p.tilesP * p.tilesQ * p.splits;
   int cap = grid_cap > 0 ? grid_cap : num_sms();
   if (grid > cap) grid = cap;
-  QR_CUDA(launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)L::kDynamic, st, tuning("pdl", 0) != 0, tmP, tmQ, p));
+  QR_CUDA(launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)L::kDynamic, st, g_tuning.pdl != 0, tmP, tmQ, p));
   return QR_OK;
 }
 
 template <typename Kern, typename... Maps>
 static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const GemmParams& p, int grid_cap,
                            cudaStream_t st, bool pdl, const Maps&... maps);
-
-template <int PST, int MODE>
-static int launch_gemm_2sm_ts(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
-  using L = SmemLayoutTS<PST>;
-  static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
-  static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_ts_kernel<PST, MODE>, kThreadsTS, L::kDynamic, max_clusters, p, grid_cap, st, false, tmP, tmQ);
-}
 
 template <int PST, int IST, int MODE>
 static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const OutMaps& tmO, const GemmParams& p,
@@ -1407,7 +954,7 @@ static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const
   static_assert(L::kStageOff % 1024 == 0, "staging blocks must be 1024-byte aligned for the 128-byte swizzle");
   static thread_local int max_clusters[64] = {0};
   return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, p, grid_cap, st,
-                         tuning("pdl", 0) != 0, tmP, tmQ, tmO);
+                         g_tuning.pdl != 0, tmP, tmQ, tmO);
 }
 
 template <typename Kern, typename... Maps>
@@ -1496,45 +1043,37 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   int* status = kernel_status_ptr();
   if (!status) return fail(QR_ENOTREADY, "%s: no CUDA device", who);
 
-  const int swap_max_m = tuning("gemm_swap_max_m", 64);
+  const int swap_max_m = g_tuning.gemm_swap_max_m;
   const bool swap = M <= swap_max_m;
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
   p.splits = 1; p.ws_partial = nullptr; p.ws_counter = nullptr;
-  p.sync_mode = tuning("gemm_sync", 7);
-  p.debug = tuning("gemm_debug", 0);
-  p.trace = reinterpret_cast<long long*>(debug_trace_ptr());
   p.bias = reinterpret_cast<const __half*>(bias);
   p.tma_out = 0; p.n_outs = 1; p.swiglu = 0;
   if (swiglu) {
-    if (swap || M <= kBM || tuning("gemm_2sm", 1) == 0 || tuning("gemm_ts", 0) != 0)
+    if (swap || M <= kBM || g_tuning.gemm_2sm == 0)
       return fail(QR_EUNSUPPORTED, "%s: served by the prefill kernel only (more than %d rows)", who, kBM);
     if (N % kBN2 != 0) return fail(QR_EINVAL, "%s: N = %lld must be a multiple of %d (interleaved gate/up rows)", who, (long long)N, kBN2);
     if (bias) return fail(QR_EUNSUPPORTED, "%s: bias is not supported", who);
     if (!aligned16(out) || ldo % 8 != 0) return fail(QR_EALIGN, "%s: output must be 16-byte aligned with ldo %% 8 == 0", who);
     if (ldo < N / 2) return fail(QR_EINVAL, "%s: ldo < N / 2", who);
   }
-  if (n_more > 0 && (swap || M <= kBM || tuning("gemm_2sm", 1) == 0 || tuning("gemm_ts", 0) != 0))
+  if (n_more > 0 && (swap || M <= kBM || g_tuning.gemm_2sm == 0))
     return fail(QR_EUNSUPPORTED, "%s: several outputs are served by the prefill kernel only (more than %d rows)", who, kBM);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
   CUtensorMap tmP, tmQ;
   int rc;
-  const int grid_cap = tuning("gemm_grid", 0);
-  if (!swap && M > kBM && tuning("gemm_2sm", 1) != 0) {
+  const int grid_cap = g_tuning.gemm_grid;
+  if (!swap && M > kBM && g_tuning.gemm_2sm != 0) {
     p.rowsP = (int)M; p.rowsQ = (int)N;
     p.tilesP = (int)((M + 2 * kBM - 1) / (2 * kBM)); p.tilesQ = (int)((N + kBN2 - 1) / kBN2);
     p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
-    const bool ts = tuning("gemm_ts", 0) != 0;
-    const int boxb = ts ? kBKBytes * kTSSub : kBKBytes;
-    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM, boxb, ts))) return rc;
-    if ((rc = make_packed_map(&tmQ, B, N, K / 2, kBN2 / 2, boxb, false))) return rc;
-    if (ts) {
-      return launch_gemm_2sm_ts<2, MODE>(tmP, tmQ, p, grid_cap, st);
-    }
+    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
+    if ((rc = make_packed_map(&tmQ, B, N, K / 2, kBN2 / 2))) return rc;
     // tiled stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element-wise
     OutMaps tmO;
-    p.tma_out = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) && tuning("gemm_tma_out", 1) != 0;
+    p.tma_out = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) && g_tuning.gemm_tma_out != 0;
     p.n_outs = 1;
     if (swiglu) {
       p.swiglu = 1; p.tma_out = 1;
@@ -1554,14 +1093,14 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
     return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, tmO, p, grid_cap, st);
   }
   if (!swap) {
-    int bn = tuning("gemm_bn", 256);
+    int bn = g_tuning.gemm_bn;
     if (bn != 256 && bn != 128 && bn != 64) bn = 256;
     p.rowsP = (int)M; p.rowsQ = (int)N;
     p.tilesP = (int)((M + kBM - 1) / kBM); p.tilesQ = (int)((N + bn - 1) / bn);
     p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
     if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
     if ((rc = make_packed_map(&tmQ, B, N, K / 2, bn))) return rc;
-    const int pst = tuning("gemm_pst", 4);
+    const int pst = g_tuning.gemm_pst;
     if (bn == 256) {
       if (pst == 3) return launch_gemm<256, 3, 3, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
       return launch_gemm<256, 4, 2, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
@@ -1570,14 +1109,14 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
     return launch_gemm<64, 6, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
   }
   // a handful of token rows: one pass over the weights on the CUDA cores, no tensor-core fixed costs
-  if (M <= tuning("gemv_max_m", 8)) {
+  if (M <= g_tuning.gemv_max_m) {
     rc = launch_gemv_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
     if (rc != QR_EUNSUPPORTED) return rc;
   }
   // decode-sized M: weights fill the MMA rows, tokens are the MMA columns; with a scratch buffer the K
   // loop of a tile is split over several CTAs so that all SMs stream weights
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-  if (ws && tuning("gemm_splitk", 1) != 0) {
+  if (ws && g_tuning.gemm_splitk != 0) {
     size_t need = 0, compact_counters = 0;
     int splits = decode_splits(M, N, K, &need, &compact_counters, !compact_ws);
     if (!compact_ws) {   // fixed counter region in front of the partial tiles
@@ -1636,14 +1175,14 @@ int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, 
 
 // scratch of the decode path (split-K) in the compact layout of the built-in array of qr_linear_i4_f16_static
 static size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  if (M <= 0 || N <= 0 || K <= 0 || M > qr::tuning("gemm_swap_max_m", 64)) return 0;
+  if (M <= 0 || N <= 0 || K <= 0 || M > qr::g_tuning.gemm_swap_max_m) return 0;
   size_t bytes = 0;
   qr::decode_splits(M, N, K, &bytes);
   return bytes;
 }
 
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  if (M <= 0 || N <= 0 || K <= 0 || M > qr::tuning("gemm_swap_max_m", 64)) return 0;
+  if (M <= 0 || N <= 0 || K <= 0 || M > qr::g_tuning.gemm_swap_max_m) return 0;
   size_t bytes = 0, compact_counters = 0;
   if (qr::decode_splits(M, N, K, &bytes, &compact_counters, true) <= 1 || compact_counters > qr::kWsCounterRegion) return 0;
   return bytes - compact_counters + qr::kWsCounterRegion;

@@ -602,7 +602,7 @@ static int launch_fast(const HadqParams& p, int threads, size_t smem, cudaStream
     if (dev < 64) configured[dev] = smem;
   }
   QR_CUDA(launch_kernel(hadq_fast_kernel<KT>, dim3(persistent_grid(p.rows, threads, smem)), dim3(threads), smem, st,
-                        tuning("pdl", 0) != 0, p));
+                        g_tuning.pdl != 0, p));
   return QR_OK;
 }
 
@@ -622,7 +622,7 @@ static int launch_generic(const HadqParams& p, cudaStream_t st) {
   if (per_sm < 1) per_sm = 1;
   int64_t grid = (int64_t)num_sms() * per_sm;
   if (grid > p.rows) grid = p.rows;
-  QR_CUDA(launch_kernel(hadq_generic_kernel<T>, dim3((int)grid), dim3(256), smem, st, tuning("pdl", 0) != 0, p));
+  QR_CUDA(launch_kernel(hadq_generic_kernel<T>, dim3((int)grid), dim3(256), smem, st, g_tuning.pdl != 0, p));
   return QR_OK;
 }
 
@@ -659,16 +659,16 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
   p.clip = clip; p.q = q; p.scales = reinterpret_cast<__half*>(scales); p.y_out = y_out; p.do_quant = do_quant;
 
   p.top_bits = 0;
-  const int forced = tuning("hadq_path", 0);  // 1 = always generic (for A/B checks)
+  const int forced = g_tuning.hadq_path;  // 1 = always generic (for A/B checks)
   const bool base_ok = (elem_size == 2) && forced != 1 && aligned16(x) && (ldx % 8 == 0) && (n % 8 == 0) &&
                        (!y_out || aligned16(y_out)) && (!do_quant || aligned16(q)) && n <= 32768;
   if (base_ok && K == 0 && do_quant && n >= 64) {
     int threads = ((n / 8 + 3) / 4 + 31) / 32 * 32;
     QR_CUDA(launch_kernel(quant_rows_kernel, dim3(persistent_grid(rows, threads, 1024)), dim3(threads), 0, st,
-                          tuning("pdl", 0) != 0, p));
+                          g_tuning.pdl != 0, p));
     return QR_OK;
   }
-  if (base_ok && K > 1 && m == 64 && ldx == n && tuning("hadq_tc", 1) != 0) {
+  if (base_ok && K > 1 && m == 64 && ldx == n && g_tuning.hadq_tc != 0) {
     const int rc = launch_hadq_tc(x, rows, n, K, had_k, clip, q, scales, y_out, do_quant, st);
     if (rc != QR_EUNSUPPORTED) return rc;
   }

@@ -40,8 +40,6 @@ struct HadqTcParams {
   __half* y_out;
   int do_quant;
   int* status;
-  long long* trace;   // optional clock64 time line of CTA 0 (debugging aid), or null
-  int debug;          // timing experiments only (results become wrong): 1 = skip the second hadK tile, 2 = 4 k steps only
 };
 
 constexpr int kTcEpiWarps = 8;        // epilogue warps per set; set r takes row r of every pair of token rows
@@ -121,7 +119,6 @@ __global__ void __launch_bounds__(kTcThreads, 1)
 hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) p.trace[512 + 7 * 64 + 2] = clock64();
   extern __shared__ unsigned char smem_dyn[];
   const uint32_t smem_base = (smem_u32(smem_dyn) + 1023u) & ~1023u;
   unsigned char* smem_gen = smem_dyn + (smem_base - smem_u32(smem_dyn));
@@ -157,10 +154,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // time line of CTA 0: [set][phase 0..7][pair index < 64]
-  auto stamp = [&](int set_, int phase, uint32_t i_) {
-    if (p.trace && blockIdx.x == 0 && i_ < 64) p.trace[set_ * 512 + phase * 64 + i_] = clock64();
-  };
   const int64_t npairs = (p.rows + 1) >> 1;
 
   if (warp != 0) {
@@ -219,7 +212,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
     }
     fence_proxy_async_smem();   // A tiles and zeroed padding were written with ordinary stores
     asm volatile("bar.sync 1, %0;" ::"n"(kTcThreads - 32) : "memory");
-    if (threadIdx.x == 32) stamp(1, 7, 0);
   }
 
   if (warp == 0) {
@@ -229,7 +221,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
       for (int64_t pair = blockIdx.x; pair < npairs; pair += gridDim.x, ++i) {
         const int s = i % kTcNB;
         if (!mbar_wait(empty_b(s), ((i / kTcNB) & 1) ^ 1, abort_flag, p.status, 31)) break;
-        stamp(0, 7, i);
         const bool two = 2 * pair + 1 < p.rows;
         mbar_expect_tx(full_b(s), (uint32_t)p.K * 128u * (two ? 2u : 1u));
         const uint32_t dst = smem_base + b_off + (2 * s) * p.b_bytes;
@@ -247,13 +238,12 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
         if (!mbar_wait(full_b(s), (i / kTcNB) & 1, abort_flag, p.status, 32)) break;
         if (!mbar_wait(acc_empty(a), ((i >> 1) & 1) ^ 1, abort_flag, p.status, 33)) break;
         tc_fence_after();
-        stamp(0, 6, i);
         // Lean issue loop (one thread; every dependent integer instruction costs several cycles): descriptors are
         // (low word, constant high word) pairs advanced by 32-bit adds.  A: k step = +32 bytes inside a 64-column
         // atom, next atom a_atom_bytes further, second hadK tile 16 KB further.  B: k step = 16 rows of 128 bytes;
         // its low word also carries the distance between the two token rows (leading byte offset).
-        const int kt_n = (p.debug & 2) ? 4 : p.KT16;
-        const bool two_tiles = p.MT > 1 && !(p.debug & 1);
+        const int kt_n = p.KT16;
+        const bool two_tiles = p.MT > 1;
         const uint32_t d0 = tmem_base + a * 256;
         uint32_t a_lo = desc_lo(smem_base);
         uint32_t b_lo = desc_lo(smem_base + b_off + (2 * s) * p.b_bytes) | ((((uint32_t)p.b_bytes >> 4) & 0x3FFFu) << 16);
@@ -273,7 +263,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
             }
           }
         }
-        stamp(0, 6, 32 + i);
         umma_commit(empty_b(s));
         umma_commit(acc_full(a));
       }
@@ -293,12 +282,9 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
       const int64_t row = 2 * pair + set;
       __half2 h[32];
       float amax = 0.0f;
-      const bool st = (ew == 0 && lane == 0);
-      if (st) stamp(set, 0, i);
       bool ok = mbar_wait(acc_full(a), (i >> 1) & 1, abort_flag, p.status, 34);
       if (!ok) break;
       tc_fence_after();
-      if (st) stamp(set, 1, i);
       if (row >= p.rows) {      // odd row count: the last pair has no second row
         tc_fence_before();
         __syncwarp();
@@ -320,7 +306,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty(a));
-        if (st) stamp(set, 2, i);
         fwht_regs_tc<64>(v);
         __half2 mx = __float2half2_rn(0.0f);
 #pragma unroll
@@ -340,7 +325,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
       } else {
         if (lane == 0) mbar_arrive(acc_empty(a));
       }
-      if (st) stamp(set, 3, i);
       if (p.do_quant) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -350,7 +334,6 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
         volatile float* slots = red + (set * 2 + (i & 1)) * kTcEpiWarps;
         if (lane == 0) { slots[ew] = amax; mbar_arrive(red_bar(set)); }
         if (!mbar_wait(red_bar(set), i & 1, abort_flag, p.status, 35)) break;
-        if (st) stamp(set, 4, i);
         float amx = 0.0f;
 #pragma unroll
         for (int w = 0; w < kTcEpiWarps; ++w) amx = fmaxf(amx, slots[w]);
@@ -371,14 +354,12 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
           qo[1] = make_uint4(w4[4], w4[5], w4[6], w4[7]);
         }
       }
-      if (st) stamp(set, 5, i);
     }
   }
 
   drain_after_abort(abort_flag);
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) stamp(1, 7, 1);
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
@@ -423,8 +404,6 @@ int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k,
   p.scale = (float)(1.0 / sqrt((double)n)); p.clip = clip; p.q = q;
   p.scales = reinterpret_cast<__half*>(scales); p.y_out = reinterpret_cast<__half*>(y_out);
   p.do_quant = do_quant; p.status = status;
-  p.trace = reinterpret_cast<long long*>(debug_trace_ptr());
-  p.debug = tuning("hadq_debug", 0);
   p.b_bytes = (p.KT16 * 16 * 128 + 1023) & ~1023;
   const int smem = p.KA * p.MT * 128 * 128 + 2 * kTcNB * p.b_bytes + 8 * kTcNumBars + 16 + 4 * kTcEpiWarps * 4 + 1024 + 64;
   if (smem > 227 * 1024) return QR_EUNSUPPORTED;
@@ -437,7 +416,7 @@ int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k,
   }
   int64_t grid = num_sms();
   if (grid > (rows + 1) / 2) grid = (rows + 1) / 2;
-  QR_CUDA(launch_kernel(hadq_tc_kernel, dim3((int)grid), dim3(kTcThreads), (size_t)smem, st, tuning("pdl", 0) != 0, tm, p));
+  QR_CUDA(launch_kernel(hadq_tc_kernel, dim3((int)grid), dim3(kTcThreads), (size_t)smem, st, g_tuning.pdl != 0, tm, p));
   return QR_OK;
 }
 

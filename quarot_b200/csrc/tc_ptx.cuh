@@ -58,33 +58,6 @@ __device__ __forceinline__ void drain_after_abort(volatile int* abort_flag) {
   }
 }
 
-// Non-suspending poll (mbarrier.test_wait): used to measure how much of a wait is wake-up latency.
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_test_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if ((i & 255u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(status, code);
-  return false;
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -205,38 +178,9 @@ __device__ __forceinline__ uint32_t mapa_cluster(uint32_t local_addr, uint32_t r
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
   return r;
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// Same arrive without an explicit cluster-scope release (the form cluster pipelines commonly use).
+// Arrive on a barrier of another CTA of the cluster (shared::cluster address from mapa_cluster).
 __device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-// Bounded wait with cluster-scope acquire (the barrier is arrived on by the peer CTA as well).
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const long long t0 = clock64();
-  for (uint32_t i = 1;; ++i) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((i & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) break;
-    }
-  }
-  *abort_flag = 1;
-  atomicExch(status, code);
-  return false;
 }
 __device__ __forceinline__ void tmem_alloc_2sm(uint32_t dst_smem, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
@@ -246,14 +190,6 @@ __device__ __forceinline__ void tmem_relinquish_2sm() {
 }
 __device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_i8_2sm(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
 }
 // cta_group::2 kind::i8 MMA with the operand descriptors given as (low word, shared high word).  ACC = 1:
 // accumulate into D; ACC = 0: overwrite D; ACC = -1: decided at run time by `accumulate`.
@@ -280,37 +216,8 @@ __device__ __forceinline__ void umma_i8_2sm_w(uint32_t d_tmem, uint32_t a_lo, ui
         : "memory");
   }
 }
-// Arrives (once) on the mbarrier at shared::cluster address `bar` when all MMAs issued so far by this
-// thread have completed; `bar` may be this CTA's own barrier or the peer's (mapa_cluster).
-__device__ __forceinline__ void umma_commit_2sm(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// A operand from tensor memory (lane = row, four int8 K values per 32-bit column), B from shared memory.
-__device__ __forceinline__ void umma_i8_2sm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// registers -> TMEM: lane i of the warp writes 32 consecutive 32-bit columns of TMEM lane (base + i);
-// returns after the store has completed (tcgen05.wait::st).
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n\t"
-      "tcgen05.wait::st.sync.aligned;"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-      : "memory");
-}
-// Same, delivered to the barrier at the same shared-memory offset in every CTA of `cta_mask`
-// (bit i = CTA rank i of the cluster).  This is a barrier signal, not a data copy.
+// Arrives (once) on the mbarrier at the same shared-memory offset in every CTA of `cta_mask` (bit i = CTA rank i
+// of the cluster) when all MMAs issued so far by this thread have completed.  A barrier signal, not a data copy.
 __device__ __forceinline__ void umma_commit_2sm_mc(uint32_t bar, uint16_t cta_mask) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                ::"r"(bar), "h"(cta_mask) : "memory");

@@ -18,11 +18,16 @@ from .quantization import Quantizer
 class HadamardQuantizer(torch.nn.Module):
     """OnlineHadamard(hadamard_dim) followed by Quantizer(input_clip_ratio), fused."""
 
-    def __init__(self, hadamard_dim, input_clip_ratio=1.0):
+    def __init__(self, hadamard_dim, input_clip_ratio=1.0, had_rem_dim=None):
         super().__init__()
         self.hadamard_dim = hadamard_dim
         self.input_clip_ratio = input_clip_ratio
-        self.rem_dim = F_had.get_hadK(hadamard_dim)[1]
+        table, self.rem_dim = F_had.get_hadK(hadamard_dim)
+        # same buffer (and state-dict key) as OnlineHadamard, so checkpoints of fused and unfused models interchange
+        if table is not None:
+            self.register_buffer("had_rem_dim", had_rem_dim if had_rem_dim is not None else table.to(torch.float16))
+        else:
+            self.had_rem_dim = None
 
     def forward(self, x):
         table = F_had.device_table(self.rem_dim, x.device) if self.rem_dim > 1 else None
@@ -41,7 +46,7 @@ def fuse_modules(model):
                     n = getattr(a, "hadamard_dim", None)
                     if n is None:
                         continue
-                    mod[i] = HadamardQuantizer(n, b.input_clip_ratio)
+                    mod[i] = HadamardQuantizer(n, b.input_clip_ratio, a.had_rem_dim)
                     mod[i + 1] = torch.nn.Identity()
                     count += 1
     return count

@@ -32,18 +32,23 @@ class Linear4bit(torch.nn.Module):
 
     @staticmethod
     def from_float(module: torch.nn.Linear, weight_scales=None):
-        """Build a Linear4bit from a float Linear whose weights are already on the int4
-        grid times `weight_scales` ([out, 1]); without scales the module keeps its
-        random initial buffers (what the upstream benchmarks rely on)."""
-        weight_matrix = module.weight.data
-        int_module = Linear4bit(module.in_features, module.out_features,
-                                bias=module.bias is not None, dtype=weight_matrix.dtype).to(weight_matrix.dtype)
-        if weight_scales is not None:
-            assert weight_scales.shape == (module.out_features, 1), 'weight_scales should have shape (out_features, 1)'
-            weight_matrix = weight_matrix.cuda()
-            int_module.weight_scales.copy_(weight_scales.to(weight_matrix.dtype))
-            int_rounded_weight = (weight_matrix / weight_scales.cuda()).round()
-            int_module.weight.copy_(pack_i4(int_rounded_weight.to(torch.int8)).cpu())
-            if module.bias is not None:
-                int_module.bias.copy_(module.bias)
-        return int_module
+        """Linear4bit with the shapes, bias flag and float dtype of `module` (quarot/nn/linear.py:58-79).
+
+        With `weight_scales` ([out_features, 1]) the float weights -- expected to lie on the int4 grid times those
+        scales already -- are divided by the scales, rounded with torch.round, packed two codes per byte and stored
+        together with the scales and the bias.  Without scales nothing is converted: the result keeps the random
+        codes and zero scales of the constructor (the upstream benchmarks build their layers this way and then
+        overwrite the scales).  The division runs on the GPU; the buffers of the result stay on the CPU.
+        """
+        w = module.weight.data
+        has_bias = module.bias is not None
+        q = Linear4bit(module.in_features, module.out_features, bias=has_bias, dtype=w.dtype).to(w.dtype)
+        if weight_scales is None:
+            return q
+        assert weight_scales.shape == (module.out_features, 1), 'weight_scales should have shape (out_features, 1)'
+        codes = torch.round(w.cuda() / weight_scales.cuda()).to(torch.int8)
+        q.weight.copy_(pack_i4(codes).cpu())
+        q.weight_scales.copy_(weight_scales.to(w.dtype))
+        if has_bias:
+            q.bias.copy_(module.bias)
+        return q

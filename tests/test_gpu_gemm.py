@@ -64,8 +64,6 @@ def test_matmul_leading_dims_and_errors():
 
 
 TILE_CONFIGS = {
-    "2sm_ts": {"gemm_ts": 1},
-    "2sm_ts_grid3": {"gemm_ts": 1, "gemm_grid": 3},
     "2sm_ss_grid3": {"gemm_grid": 3},
     "2sm_ss_elementwise_stores": {"gemm_tma_out": 0},
     "1sm_bn256": {"gemm_2sm": 0},
@@ -74,7 +72,7 @@ TILE_CONFIGS = {
     "1sm_pst3": {"gemm_2sm": 0, "gemm_pst": 3},
     "1sm_grid3": {"gemm_2sm": 0, "gemm_grid": 3},
 }
-TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_ts": 0, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0, "gemm_tma_out": 1}
+TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0, "gemm_tma_out": 1}
 
 
 @pytest.mark.parametrize("tiles", sorted(TILE_CONFIGS))
