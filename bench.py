@@ -5,7 +5,7 @@
 
 A "step" is one pass over the linears of one decoder layer for one batch of
 token rows: per linear, kernel (a) (fused [Hadamard ->] absmax -> int4 pack) and
-kernel (b) (tcgen05 int4 GEMM with the dequant epilogue).  The default workload is
+kernel (b) (int4 GEMM with the dequant epilogue).  The default workload is
 the LLaMA-2-7B layer at prefill size (M = 2048 tokens): QKV 4096->12288, o_proj
 4096->4096, gate/up 4096->22016 (quantiser only) and down_proj 11008->4096 with
 the online Hadamard had_172 (x) Walsh_64.  Activations and weights are seeded
@@ -15,8 +15,14 @@ N > 1 (launched with torch.distributed.run, one rank per GPU): token rows are
 sharded, weights replicated, no collective on the data path; every rank processes
 M rows per step (weak scaling) and the reported value is the whole-job aggregate.
 
-One JSON line is printed by rank 0.  --impl reference times the CPU restatement of
-the upstream torch path (oracle/) on the host cores for the same metric and config.
+One JSON line is printed by rank 0.  Beside the headline it carries `other_configs`:
+short device-timed runs of the remaining benchmark configurations (single linear,
+decode at M = 1/8/32/64, the 70B layer; for N > 1 the 70B layer with its rows split
+over the ranks and the 70B MLP with its output channels split over the ranks) and,
+for N > 1, a `parity` block that compares the multi-GPU results with the single-GPU
+result on a small shape.  --impl reference times the CPU restatement of the upstream
+torch path (oracle/) on the host cores for the same metric and config; that arm does
+not import the product package.
 """
 import argparse
 import json
@@ -33,6 +39,17 @@ if ROOT not in sys.path:
 
 import torch  # noqa: E402
 
+# (name, K, N, online Hadamard on K?) per linear of one decoder layer -- the same tables as quarot_b200/synth.py
+# (tests/test_package_cpu.py keeps them equal); repeated here so that the reference arm needs no product import.
+LAYERS = {
+    "LLAMA2_7B": (("qkv", 4096, 12288, False), ("o_proj", 4096, 4096, False),
+                  ("gate_up", 4096, 22016, False), ("down", 11008, 4096, True)),
+    "LLAMA2_70B": (("qkv", 8192, 10240, False), ("o_proj", 8192, 8192, False),
+                   ("gate_up", 8192, 57344, False), ("down", 28672, 8192, True)),
+    "LLAMA2_70B_MLP": (("gate_up", 8192, 57344, False), ("down", 28672, 8192, True)),
+    "LLAMA2_7B_MLP": (("gate_up", 4096, 22016, False), ("down", 11008, 4096, True)),
+    "CONFIG0": (("cfg0", 4096, 4096, True),),
+}
 WORKLOADS = {
     # name: (layer table name, default tokens per GPU)
     "llama2_7b_prefill": ("LLAMA2_7B", 2048),
@@ -50,6 +67,12 @@ WORKLOADS = {
     "llama2_7b_rmsnorm_quant": ("LLAMA2_7B", 2048),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+NOMINAL_INT8_TOPS = 4500.0
+DECODE_MAX_M = 128      # workloads with at most this many token rows are reported against the HBM roofline
+
+# DRAM traffic per launch of the dominant kernel, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum);
+# the capture behind every entry is summarised in profiles/.  Key: (workload, tokens per GPU).
+NCU_TRAFFIC_BYTES = {}
 
 
 def load_peaks():
@@ -100,7 +123,18 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def window(self, t0, t1):
+        """Median SM MHz of the samples taken between two perf_counter stamps."""
+        vals = []
+        for (t, line) in self.lines:
+            if t0 <= t <= t1:
+                try:
+                    vals.append(float(line.split(",")[0]))
+                except ValueError:
+                    pass
+        return statistics.median(vals) if vals else None
 
     def stop(self):
         if self.proc is None:
@@ -112,7 +146,7 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in self.lines:
+        for (_, line) in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -130,29 +164,47 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------ reference (CPU) arm
-def cpu_reference_run(layers, M_full, steps, warmup, budget_s=20.0):
+def _cpu_activations(O, M, K, seed):
+    """Outlier-Gaussian fp16 activations: the generator of quarot_b200/synth.py, restated for the CPU arm."""
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g, dtype=torch.float32)
+    idx = torch.randperm(K, generator=g)[: min(8, K)]
+    x[:, idx] *= 50.0
+    return x.to(torch.float16)
+
+
+def _cpu_weights(O, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    codes = torch.randint(-8, 8, (N, K), generator=g, dtype=torch.int8)
+    scales = (torch.rand(N, 1, generator=g) * 0.015 + 0.005).to(torch.float16)
+    return O.pack_i4(codes), scales
+
+
+def cpu_reference_run(layers, M_full, steps, warmup, budget_s=20.0, rows=None):
     """Times the CPU restatement of the upstream torch path on a bounded sample of token rows.
 
     Weights are unpacked to int32 once, outside the timed region (as the fake-quant
     reference keeps them); per step and per linear: Hadamard (fp32 butterflies, cast
     to fp16), per-token scale, quantise, pack, unpack, int32 matmul, fp32 dequant.
+    Imports only oracle/, never the product package.
     """
     from oracle import quarot_oracle as O
-    from quarot_b200 import synth
     cores = torch.get_num_threads()
-    # pick the sample so that one step costs about budget_s / (steps + warmup)
-    a = torch.randint(-8, 8, (16, 4096), dtype=torch.int32)
-    b = torch.randint(-8, 8, (1024, 4096), dtype=torch.int32)
-    t0 = time.perf_counter()
-    _ = a @ b.T
-    rate = 2.0 * 16 * 1024 * 4096 / max(time.perf_counter() - t0, 1e-6)   # int ops / s
-    per_token_ops = layer_ops(layers, 1)
-    target = budget_s / max(steps + warmup, 1)
-    ms = int(max(1, min(64, M_full, rate * target / per_token_ops)))
+    if rows is None:
+        # pick the sample so that one step costs about budget_s / (steps + warmup)
+        a = torch.randint(-8, 8, (16, 4096), dtype=torch.int32)
+        b = torch.randint(-8, 8, (1024, 4096), dtype=torch.int32)
+        t0 = time.perf_counter()
+        _ = a @ b.T
+        rate = 2.0 * 16 * 1024 * 4096 / max(time.perf_counter() - t0, 1e-6)   # int ops / s
+        per_token_ops = layer_ops(layers, 1)
+        target = budget_s / max(steps + warmup, 1)
+        rows = int(max(1, min(64, M_full, rate * target / per_token_ops)))
+    ms = rows
     data = []
     for (name, K, N, had) in layers:
-        x = synth.activations(ms, K, seed=1234)
-        w, sw = synth.weights(N, K, seed=4321)
+        x = _cpu_activations(O, ms, K, seed=1234)
+        w, sw = _cpu_weights(O, N, K, seed=4321)
         data.append((x, O.unpack_i4(w), sw, had))
 
     def step():
@@ -175,12 +227,11 @@ def cpu_reference_run(layers, M_full, steps, warmup, budget_s=20.0):
     return {"value": tops, "unit": "TOPS", "cores": cores, "kind": "port",
             "sample": "%d of %d token rows per step, %d steps; weights pre-unpacked to int32 outside the "
                       "timed region; ms_per_step is scaled linearly to %d rows" % (ms, M_full, steps, M_full),
-            "ms_per_step_full": dt * 1e3 * (M_full / ms), "tokens_per_s": ms / dt}
+            "ms_per_step_full": dt * 1e3 * (M_full / ms), "ms_per_step_sample": dt * 1e3, "tokens_per_s": ms / dt}
 
 
 # ------------------------------------------------------------------ device arm
 def build_device_workload(layers, M, dev, nsets):
-    import quarot_b200 as qb
     from quarot_b200 import synth
     from quarot_b200.functional import hadamard as FH
     work = []
@@ -199,24 +250,171 @@ def build_device_workload(layers, M, dev, nsets):
     return work
 
 
-def device_step(qb, work, set_idx, record=None):
+def fused_quant_rows():
+    """Largest M for which Sequential(Quantizer, Linear4bit) runs as ONE launch (quantiser inside the GEMV)."""
+    from quarot_b200.nn import fused
+    return fused.QuantLinear4bit.FUSED_MAX_ROWS
+
+
+def device_step(qb, work, set_idx, part="all"):
+    """One step.  part = "all" | "quant" (kernel (a) launches only) | "gemm" (kernel (b) launches only; the packed
+    activations of the last full step are reused).  Returns the number of kernels launched."""
+    launches = 0
+    M = work[0]["x"][0].shape[0]
+    fuse = M <= fused_quant_rows()
     for L in work:
-        if record is not None:
-            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
-            e0.record()
-        if L["khad"] == 0 and L["x"][set_idx].shape[0] <= 2:
-            # one or two token rows, no transform: the quantiser runs inside the weight-streaming kernel (one launch)
-            if record is not None:
-                e1.record()
-            qb.quant_linear_i4(L["x"][set_idx], L["w"][set_idx], L["sw"][set_idx], out=L["out"])
-        else:
+        if L["khad"] == 0 and fuse:
+            # a few token rows, no transform: the quantiser runs inside the weight-streaming kernel (one launch)
+            if part != "quant":
+                qb.quant_linear_i4(L["x"][set_idx], L["w"][set_idx], L["sw"][set_idx], out=L["out"])
+                launches += 1
+            continue
+        if part != "gemm":
             qb.hadamard_quant(L["x"][set_idx], L["table"], L["khad"], 1.0, out_q=L["q"], out_s=L["s"])
-            if record is not None:
-                e1.record()
+            launches += 1
+        if part != "quant":
             qb.linear_i4(L["q"], L["s"], L["w"][set_idx], L["sw"][set_idx], out=L["out"])
-        if record is not None:
-            e2.record()
-            record.append((L["name"], e0, e1, e2))
+            launches += 1
+    return launches
+
+
+def capture_graphs(dev, nsets, fn):
+    """One CUDA graph per buffer set of fn(set_idx); None when capture is not possible."""
+    try:
+        graphs = []
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for sidx in range(nsets):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    fn(sidx)
+                graphs.append(g)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        return graphs
+    except Exception as exc:   # capture is an optimisation of the harness, not of the kernels
+        sys.stderr.write("bench.py: CUDA graph capture failed (%s); timing eager launches\n" % exc)
+        torch.cuda.synchronize(dev)
+        return None
+
+
+def timed_steps(dev, dist, run, steps, warmup):
+    """ms per step of run(i), CUDA events on the current stream, barrier + synchronize on both sides, max over ranks."""
+    for i in range(warmup):
+        run(i)
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(steps):
+        run(i)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    t1 = time.perf_counter()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms, (t0, t1)
+
+
+def measure_layers(qb, layers, M, dev, dist, steps, warmup, use_graph=True, breakdown=True, nsets=3):
+    """Device-timed step of `layers` at M token rows: whole step, and kernel (a) / kernel (b) launches alone
+    (each as its own graph replay, so the split is free of Python launch time)."""
+    work = build_device_workload(layers, M, dev, nsets)
+    for i in range(nsets):
+        device_step(qb, work, i)
+    torch.cuda.synchronize(dev)
+    res = {"work": work}
+
+    def runner(part):
+        graphs = capture_graphs(dev, nsets, lambda s: device_step(qb, work, s, part)) if use_graph else None
+        if graphs is not None:
+            return (lambda i: graphs[i % nsets].replay()), True
+        return (lambda i: device_step(qb, work, i % nsets, part)), False
+
+    run_all, graphed = runner("all")
+    res["launch_mode"] = "cuda_graph_replay" if graphed else "eager"
+    res["run_all"] = run_all
+    res["ms_step"], res["window"] = timed_steps(dev, dist, run_all, steps, warmup)
+    res["launches_per_step"] = device_step(qb, work, 0)
+    if breakdown:
+        run_g, _ = runner("gemm")
+        res["gemm_ms"], _ = timed_steps(dev, None, run_g, steps, warmup)
+        res["gemm_launches"] = device_step(qb, work, 0, "gemm")
+        res["quant_launches"] = device_step(qb, work, 0, "quant")
+        if res["quant_launches"]:
+            run_q, _ = runner("quant")
+            res["quant_ms"], _ = timed_steps(dev, None, run_q, steps, warmup)
+        else:
+            res["quant_ms"] = 0.0
+        device_step(qb, work, 0)      # leave q / s consistent
+    torch.cuda.synchronize(dev)
+    return res
+
+
+def roofline_record(layers, M, res, peaks, peak_src, workload, int8_probe, region_s):
+    """`roofline` of the dominant kernel, kernel (b): tensor-bound at prefill sizes, HBM-bound at decode sizes."""
+    fused = M <= fused_quant_rows()
+    if M <= DECODE_MAX_M:
+        nbytes = sum(bytes_gemm(M, K, N) + (2.0 * M * K - M * K / 2.0 if (fused and not had) else 0.0)
+                     for (_, K, N, had) in layers)
+        achieved = nbytes / (res["gemm_ms"] * 1e-3) / 1e9
+        rec = {"bound": "hbm", "kernel": "decode_mma_kernel / gemm_i4_kernel<swap> (one launch per linear)",
+               "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+               "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peak_src,
+               "algorithmic_bytes_per_step": nbytes, "kernel_ms_per_step": res["gemm_ms"],
+               "frac_of_nominal_8000": achieved / 8000.0}
+    else:
+        ops = layer_ops(layers, M)
+        achieved = ops / (res["gemm_ms"] * 1e-3) / 1e12
+        burst, sustained = 2.0 * peaks["bf16_tflops"], 2.0 * peaks["bf16_tflops_sustained"]
+        use_burst = region_s < 1.0
+        peak = burst if use_burst else sustained
+        rec = {"bound": "tensor", "kernel": "gemm_i4_2sm_kernel (one launch per linear)",
+               "achieved": achieved, "peak": peak, "unit": "TOPS", "frac": achieved / peak,
+               "peak_source": "2 x %s of MEASURED_PEAKS.json (%s): dense int8 runs at twice the bf16 rate on these tensor "
+                              "cores and the file holds no int8 figure; the timed region lasted %.3f s, so the %s figure "
+                              "applies" % ("bf16_tflops" if use_burst else "bf16_tflops_sustained", peak_src, region_s,
+                                           "burst" if use_burst else "sustained"),
+               "peak_burst_2x_bf16": burst, "peak_sustained_2x_bf16": sustained,
+               "int8_measured_tops": int8_probe, "frac_of_int8_measured": (achieved / int8_probe) if int8_probe else None,
+               "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
+               "peak_exceeded": bool(achieved > peak),
+               "kernel_ms_per_step": res["gemm_ms"]}
+    traffic = NCU_TRAFFIC_BYTES.get((workload, M))
+    rec["traffic"] = traffic
+    return rec
+
+
+def int8_probe_tops(dev):
+    """Dense int8 GEMM rate of the library on this GPU (torch._int_mm, 8192^3), as a cross-check of the peak."""
+    try:
+        a = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device=dev)
+        b = torch.randint(-8, 8, (8192, 8192), dtype=torch.int8, device=dev).t()
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize(dev)
+        best = None
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            torch.cuda.synchronize(dev)
+            ms = e0.elapsed_time(e1)
+            best = ms if best is None else min(best, ms)
+        return 2.0 * 8192 ** 3 / (best * 1e-3) / 1e12
+    except Exception as exc:
+        sys.stderr.write("bench.py: int8 probe skipped (%r)\n" % (exc,))
+        return None
 
 
 def e2e_run(qb, layers, M, dev, steps, warmup, work):
@@ -263,6 +461,22 @@ def e2e_run(qb, layers, M, dev, steps, warmup, work):
         fin.record(s_out)
         main.wait_event(fin)
 
+    def copies_only(which):
+        """The step's host copies alone, one direction at a time: what the host link gives this rank."""
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        douts = [torch.empty((M, L["N"]), dtype=torch.float16, device=dev) for L in work] if which == "d2h" else None
+        torch.cuda.synchronize(dev)
+        e0.record(main)
+        for _ in range(3):
+            for i in range(len(work)):
+                if which == "h2d":
+                    dx[i].copy_(hx[i], non_blocking=True)
+                else:
+                    hout[i].copy_(douts[i], non_blocking=True)
+        e1.record(main)
+        torch.cuda.synchronize(dev)
+        return e0.elapsed_time(e1) / 3
+
     for _ in range(warmup):
         step()
     torch.cuda.synchronize(dev)
@@ -272,10 +486,12 @@ def e2e_run(qb, layers, M, dev, steps, warmup, work):
         step()
     e1.record(main)
     torch.cuda.synchronize(dev)
-    return e0.elapsed_time(e1) / steps, h2d_bytes, d2h_bytes
+    ms = e0.elapsed_time(e1) / steps
+    h2d_ms, d2h_ms = copies_only("h2d"), copies_only("d2h")
+    return ms, h2d_bytes, d2h_bytes, h2d_ms, d2h_ms
 
 
-def colsplit_run(args, layers, M, dev, world, rank, dist):
+def colsplit_run(steps, warmup, layers, M, dev, world, rank, dist):
     """Column split: rank r owns N/G output channels of each linear; kernel (a) runs on all M rows on every
     rank, the local GEMM produces [M, N/G], the slabs are all-gathered and interleaved into [M, N].
     Times the local compute alone and compute + collective (CUDA events, max over ranks)."""
@@ -330,24 +546,58 @@ def colsplit_run(args, layers, M, dev, world, rank, dist):
     if fused is not None:
         modes.append(("fused_peer_store_ms", "fused"))
     for label, coll in modes:
-        for _ in range(max(args.warmup, 3)):
-            step(coll)
-        torch.cuda.synchronize(dev)
-        if dist is not None:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            step(coll)
-        e1.record()
-        torch.cuda.synchronize(dev)
-        ms = e0.elapsed_time(e1) / args.steps
-        if dist is not None:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        res[label] = ms
+        res[label], _ = timed_steps(dev, dist, lambda i: step(coll), steps, max(warmup, 3))
     return res
+
+
+def colsplit_line_parts(res, layers, M, n_gpus):
+    ops = layer_ops(layers, M)           # whole job: every output channel is computed exactly once
+    tops = lambda t: ops / (t * 1e-3) / 1e12
+    exchanged = sum(2 * M * (N // n_gpus) * (n_gpus - 1) for (_, _, N, _) in layers)
+    out = {"compute_only": {"ms_per_step": res["compute_ms"], "value": tops(res["compute_ms"]), "unit": "TOPS"},
+           "nccl_allgather": {"ms_per_step": res["compute_plus_allgather_ms"],
+                              "value": tops(res["compute_plus_allgather_ms"]), "unit": "TOPS"},
+           "fused_peer_store": None, "exchanged_bytes_per_rank": exchanged}
+    if "fused_peer_store_ms" in res:
+        t = res["fused_peer_store_ms"]
+        out["fused_peer_store"] = {"ms_per_step": t, "value": tops(t), "unit": "TOPS",
+                                   "nvlink_out_gbs_per_rank": exchanged / (t * 1e-3) / 1e9}
+    return out
+
+
+def multi_gpu_parity(dev, world, rank, dist):
+    """Small-shape equality checks of the multi-GPU forms against the single-GPU result (outside any timed region):
+    row sharding, column split with the NCCL all-gather, column split with the epilogue storing into the peers."""
+    import quarot_b200 as qb
+    from quarot_b200 import dist as qd, synth
+    M, K, N = 64 * world + 192, 1024, 512 * world
+    x = synth.activations(M, K, seed=5).to(dev)
+    w, sw = synth.weights(N, K, seed=6)
+    w, sw = w.to(dev), sw.to(dev)
+    q, s, _ = qb.hadamard_quant(x, None, 0, 1.0)
+    single = qb.linear_i4(q, s, w, sw)
+    out = {}
+    lo, hi = qd.shard_rows(M, world, rank)
+    ql, sl, _ = qb.hadamard_quant(x[lo:hi].contiguous(), None, 0, 1.0)
+    rows = qd.gather_rows(qb.linear_i4(ql, sl, w, sw), M)
+    out["row_sharded"] = bool(torch.equal(rows, single))
+    pq = qb.PackedQuantizedTensor(q, s)
+    col = qd.ColumnSplitLinear4bit(w, sw.view(-1, 1))
+    out["column_split_nccl_allgather"] = bool(torch.equal(col(pq).view(M, N), single))
+    try:
+        fused = qd.FusedColumnSplitLinear4bit(w, sw.view(-1, 1))
+        target = qd.SymmetricOutput(M, N, dev)
+        ok = True
+        for _ in range(2):
+            ok = ok and bool(torch.equal(fused(pq, target), single))
+        out["column_split_fused_peer_store"] = ok
+    except Exception as exc:
+        out["column_split_fused_peer_store"] = "skipped: %r" % (exc,)
+    flags = torch.tensor([1 if v is True or isinstance(v, str) else 0 for v in out.values()], device=dev)
+    dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+    out["all_ranks_ok"] = bool(int(flags.min()) == 1)
+    out["shape"] = {"M": M, "K": K, "N": N}
+    return out
 
 
 def mlp_run(args, layers, M, dev):
@@ -380,16 +630,7 @@ def mlp_run(args, layers, M, dev):
 
     res = {}
     for label, fused in (("unfused_ms", False), ("fused_ms", True)):
-        for i in range(max(args.warmup, nsets)):
-            step(i % nsets, fused)
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            step(i % nsets, fused)
-        e1.record()
-        torch.cuda.synchronize(dev)
-        res[label] = e0.elapsed_time(e1) / args.steps
+        res[label], _ = timed_steps(dev, None, lambda i: step(i % nsets, fused), args.steps, max(args.warmup, nsets))
     return res
 
 
@@ -405,17 +646,73 @@ def norm_run(args, M, K, dev):
     norm, quant = qb.nn.RMSNorm(K), qb.nn.Quantizer()
     res = {}
     for label, fn in (("unfused_ms", lambda x: quant(norm(x))), ("fused_ms", fused)):
-        for i in range(max(args.warmup, 3)):
-            fn(xs[i % nsets])
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(args.steps):
-            fn(xs[i % nsets])
-        e1.record()
-        torch.cuda.synchronize(dev)
-        res[label] = e0.elapsed_time(e1) / args.steps
+        res[label], _ = timed_steps(dev, None, lambda i: fn(xs[i % nsets]), args.steps, max(args.warmup, 3))
     return res
+
+
+def heads_hadamard_run(dev, steps, warmup):
+    """The small online Hadamard over the heads axis in front of o_proj (a transposed view [B, S, head_dim, heads],
+    n = 32 for LLaMA-2-7B): read + write of the [2048, 4096] fp16 attention output."""
+    import quarot_b200 as qb
+    M, heads, hd = 2048, 32, 128
+    had = qb.nn.OnlineHadamard(heads)
+    xs = [torch.randn(1, M, heads, hd, device=dev, dtype=torch.float16) for _ in range(12)]
+    ms, _ = timed_steps(dev, None, lambda i: had(xs[i % 12].transpose(-1, -2)), steps, warmup)
+    nbytes = 2.0 * 2 * M * heads * hd
+    return {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "shape": [1, M, heads, hd], "launch_mode": "eager"}
+
+
+def other_configs(qb, dev, dist, world, rank, peaks, peak_src, headline_workload, int8_probe):
+    """Short device-timed runs of the benchmark configurations that are not the headline."""
+    out = {}
+    steps, warmup = 10, 3
+
+    def one(name, table, M, st=steps):
+        layers = LAYERS[table]
+        r = measure_layers(qb, layers, M, dev, None, st, warmup)
+        ops = layer_ops(layers, M)
+        rec = {"tokens": M, "ms_per_step": r["ms_step"], "value": ops / (r["ms_step"] * 1e-3) / 1e12, "unit": "TOPS",
+               "tokens_per_s": M / (r["ms_step"] * 1e-3), "kernel_b_ms": r["gemm_ms"], "kernel_a_ms": r["quant_ms"],
+               "launches_per_step": r["launches_per_step"], "launch_mode": r["launch_mode"],
+               "roofline": roofline_record(layers, M, r, peaks, peak_src, name, int8_probe, st * r["ms_step"] * 1e-3)}
+        if M > DECODE_MAX_M and r["quant_ms"]:
+            qbytes = sum(bytes_quant(M, K) for (_, K, _, _) in layers)
+            rec["kernel_a_gbs"] = qbytes / (r["quant_ms"] * 1e-3) / 1e9
+        del r
+        torch.cuda.empty_cache()
+        return rec
+
+    if headline_workload != "config0":
+        out["config0"] = one("config0", "CONFIG0", 2048, 20)
+    if headline_workload != "llama2_7b_prefill":
+        out["llama2_7b_prefill"] = one("llama2_7b_prefill", "LLAMA2_7B", 2048)
+    for m in (1, 8, 32, 64):
+        out["llama2_7b_decode_m%d" % m] = one("llama2_7b_decode", "LLAMA2_7B", m, 30)
+    if headline_workload != "llama2_70b_prefill":
+        out["llama2_70b_prefill"] = one("llama2_70b_prefill", "LLAMA2_70B", 4096, 5)
+    try:
+        out["heads_axis_hadamard_n32"] = heads_hadamard_run(dev, 30, 5)
+    except Exception as exc:
+        out["heads_axis_hadamard_n32"] = {"skipped": repr(exc)}
+    if world > 1:
+        # strong scaling of the 70B layer: the 4096 token rows are split over the ranks
+        layers = LAYERS["LLAMA2_70B"]
+        m_loc = 4096 // world
+        r = measure_layers(qb, layers, m_loc, dev, dist, 5, warmup, breakdown=False)
+        ops = layer_ops(layers, 4096)
+        out["llama2_70b_prefill_rows_split"] = {
+            "tokens_total": 4096, "tokens_per_gpu": m_loc, "ms_per_step": r["ms_step"], "scaling": "strong",
+            "value": ops / (r["ms_step"] * 1e-3) / 1e12, "unit": "TOPS", "tokens_per_s": 4096 / (r["ms_step"] * 1e-3)}
+        del r
+        torch.cuda.empty_cache()
+        layers = LAYERS["LLAMA2_70B_MLP"]
+        for m in (256, 4096):
+            res = colsplit_run(5, 3, layers, m, dev, world, rank, dist)
+            rec = colsplit_line_parts(res, layers, m, world)
+            rec["tokens"] = m
+            out["llama2_70b_mlp_colsplit_m%d" % m] = rec
+            torch.cuda.empty_cache()
+    return out
 
 
 def main():
@@ -429,13 +726,13 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-others", action="store_true", help="skip other_configs, the sustained run and the parity block")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
 
-    from quarot_b200 import synth
     table_name, default_m = WORKLOADS[args.workload]
-    layers = getattr(synth, table_name)
+    layers = LAYERS[table_name]
     M = args.tokens or default_m
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -459,15 +756,23 @@ def main():
                 "config": config, "tokens_per_s": r["tokens_per_s"],
                 "cpu_baseline": {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")},
                 "e2e": {"value": r["value"], "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        if not args.no_others:
+            # the single-linear configuration (M 2048, K 4096, N 4096) timed in full, one step, no extrapolation
+            c0 = cpu_reference_run(LAYERS["CONFIG0"], 2048, 1, 0, rows=2048)
+            line["config0_in_full"] = {"ms_per_step": c0["ms_per_step_sample"], "value": c0["value"], "unit": "TOPS",
+                                       "tokens": 2048, "cores": c0["cores"]}
         print(json.dumps(line))
         return 0
 
     # ------------------------------------------------------------ our arm (GPU)
     import quarot_b200 as qb
     from quarot_b200 import _lib
-    for kv in filter(None, os.environ.get("QR_TUNE", "").split(",")):   # experiments: QR_TUNE=gemm_2sm=0,gemm_pst=6
+    for kv in filter(None, os.environ.get("QR_TUNE", "").split(",")):   # kernel-selection knobs: QR_TUNE=gemm_2sm=0,pdl=1
         k, v = kv.split("=")
-        _lib.set_tuning(k, int(v))
+        if k == "fused_max_rows":
+            qb.nn.fused.QuantLinear4bit.FUSED_MAX_ROWS = int(v)
+        else:
+            _lib.set_tuning(k, int(v))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
     dev = torch.device("cuda", local_rank)
@@ -508,13 +813,13 @@ def main():
         return 0
 
     if args.workload == "llama2_70b_mlp_colsplit":
-        res = colsplit_run(args, layers, M, dev, world, rank, dist)
-        ops = layer_ops(layers, M)           # whole job: every output channel is computed exactly once
+        res = colsplit_run(args.steps, args.warmup, layers, M, dev, world, rank, dist)
+        parts = colsplit_line_parts(res, layers, M, n_gpus)
         # headline: the epilogue that stores into the peers' matrices where it ran (N > 1 with symmetric memory),
         # else compute + NCCL all-gather; the other variants are reported beside it
         ms = res.get("fused_peer_store_ms", res["compute_plus_allgather_ms"])
-        tops = lambda t: ops / (t * 1e-3) / 1e12
-        line = {"metric": metric, "value": tops(ms), "unit": "TOPS", "n_gpus": n_gpus,
+        ops = layer_ops(layers, M)
+        line = {"metric": metric, "value": ops / (ms * 1e-3) / 1e12, "unit": "TOPS", "n_gpus": n_gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
                 "scaling": "strong", "vs_baseline": None,
                 "dtype": "int4 codes widened to int8, int32 accumulate, fp16 out", "data": "synthetic",
@@ -522,129 +827,85 @@ def main():
                                                 "result assembled on every rank by " +
                                                 ("tiled stores of the GEMM epilogue into the peers' matrices (NVLink)"
                                                  if "fused_peer_store_ms" in res else "an NCCL all-gather of the fp16 slabs")),
-                "compute_only": {"ms_per_step": res["compute_ms"], "value": tops(res["compute_ms"]), "unit": "TOPS"},
-                "nccl_allgather": {"ms_per_step": res["compute_plus_allgather_ms"],
-                                   "value": tops(res["compute_plus_allgather_ms"]), "unit": "TOPS"},
-                "fused_peer_store": (None if "fused_peer_store_ms" not in res else
-                                     {"ms_per_step": res["fused_peer_store_ms"], "value": tops(res["fused_peer_store_ms"]),
-                                      "unit": "TOPS"}),
-                "exchanged_bytes_per_rank": sum(2 * M * (N // n_gpus) * (n_gpus - 1) for (_, _, N, _) in layers),
                 "tokens_per_s": M / (ms * 1e-3), "gpu_launches": 2 * len(layers) * args.steps}
+        line.update(parts)
+        if dist is not None and not args.no_others:
+            line["parity"] = multi_gpu_parity(dev, world, rank, dist)
         if rank == 0:
             print(json.dumps(line))
         if dist is not None:
             dist.destroy_process_group()
         return 0
 
-    nsets = 3
-    work = build_device_workload(layers, M, dev, nsets)
-    for i in range(max(args.warmup, nsets)):
-        device_step(qb, work, i % nsets)
-    torch.cuda.synchronize(dev)
-    # The eight launches of a step are captured once per buffer set into CUDA graphs and replayed, so the
-    # timed region measures the kernels and not the Python launch path (--no-graph times eager launches).
-    graphs = None
-    if not args.no_graph:
-        try:
-            graphs = []
-            side = torch.cuda.Stream(dev)
-            side.wait_stream(torch.cuda.current_stream(dev))
-            with torch.cuda.stream(side):
-                for sidx in range(nsets):
-                    g = torch.cuda.CUDAGraph()
-                    with torch.cuda.graph(g, stream=side):
-                        device_step(qb, work, sidx)
-                    graphs.append(g)
-            torch.cuda.current_stream(dev).wait_stream(side)
-            for i in range(args.warmup):
-                graphs[i % nsets].replay()
-            torch.cuda.synchronize(dev)
-        except Exception as exc:   # capture is an optimisation of the harness, not of the kernels
-            sys.stderr.write("bench.py: CUDA graph capture failed (%s); timing eager launches\n" % exc)
-            graphs = None
-            torch.cuda.synchronize(dev)
-    if dist is not None:
-        dist.barrier()
+    peaks, peak_src = load_peaks()
+    int8_probe = int8_probe_tops(dev)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.25)
-    torch.cuda.synchronize(dev)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(args.steps):
-        if graphs is not None:
-            graphs[i % nsets].replay()
-        else:
-            device_step(qb, work, i % nsets)
-    e1.record()
-    torch.cuda.synchronize(dev)
-    if dist is not None:
-        dist.barrier()
-    ms_step = e0.elapsed_time(e1) / args.steps
-    if dist is not None:
-        t = torch.tensor([ms_step], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_step = float(t.item())
+    res = measure_layers(qb, layers, M, dev, dist, args.steps, args.warmup, use_graph=not args.no_graph)
+    ms_step = res["ms_step"]
+    work = res["work"]
 
-    # instrumented pass over the same steps: CUDA events around every kernel of the timed region
-    rec = []
-    for i in range(args.steps):
-        device_step(qb, work, i % nsets, record=rec)
-    torch.cuda.synchronize(dev)
+    # the same graphs replayed for about three seconds: what the kernels sustain once clocks and power settle; the
+    # median SM clock sampled meanwhile lets the clock dependence be read (time x MHz) without touching any setting
+    sustained = None
+    if not args.no_others:
+        n_sus = max(args.steps, int(3000.0 / max(ms_step, 1e-3)))
+        sus_ms, win = timed_steps(dev, dist, res["run_all"], n_sus, 0)
+        mhz = sampler.window(*win) if sampler else None
+        sustained = {"ms_per_step": sus_ms, "steps": n_sus, "seconds": n_sus * sus_ms * 1e-3,
+                     "value": layer_ops(layers, M) * n_gpus / (sus_ms * 1e-3) / 1e12, "unit": "TOPS",
+                     "sm_mhz_median": mhz, "ms_times_mhz": (sus_ms * mhz) if mhz else None}
+    burst_mhz = sampler.window(*res["window"]) if sampler else None
     clocks = sampler.stop() if sampler else None
-    per = {}
-    for (name, a, b, c) in rec:
-        d = per.setdefault(name, {"quant_ms": 0.0, "gemm_ms": 0.0, "n": 0})
-        d["quant_ms"] += a.elapsed_time(b)
-        d["gemm_ms"] += b.elapsed_time(c)
-        d["n"] += 1
-    for d in per.values():
-        d["quant_ms"] /= d["n"]
-        d["gemm_ms"] /= d["n"]
+    if clocks is not None:
+        clocks["sm_mhz_timed_region"] = burst_mhz
     status = _lib.kernel_status()
     if status != 0:
         raise SystemExit("bench.py: a kernel reported a wait timeout (status %d)" % status)
 
     total_ops = layer_ops(layers, M) * n_gpus
     value = total_ops / (ms_step * 1e-3) / 1e12
-    peaks, peak_src = load_peaks()
-    gemm_ms_total = sum(per[n]["gemm_ms"] for (n, _, _, _) in layers)
-    quant_ms_total = sum(per[n]["quant_ms"] for (n, _, _, _) in layers)
-    gemm_ops = layer_ops(layers, M)
-    int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
-    achieved = gemm_ops / (gemm_ms_total * 1e-3) / 1e12
-    roofline = {"bound": "tensor", "kernel": "gemm_i4_kernel (4 launches per step, one per linear)",
-                "achieved": achieved, "peak": int8_peak, "unit": "TOPS", "frac": achieved / int8_peak,
-                "peak_source": "2 x bf16_tflops_sustained of MEASURED_PEAKS.json (%s): dense int8 runs at twice the "
-                               "bf16 rate on these tensor cores; no int8 figure is in that file" % peak_src,
-                "traffic": None,
-                "frac_of_nominal_4500": achieved / 4500.0}
-    qbytes = sum(bytes_quant(M, K) for (_, K, _, _) in layers)
-    quant_gbs = qbytes / (quant_ms_total * 1e-3) / 1e9
+    roofline = roofline_record(layers, M, res, peaks, peak_src, args.workload, int8_probe, args.steps * ms_step * 1e-3)
     line = {"metric": metric, "value": value, "unit": "TOPS", "n_gpus": n_gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "int4 codes widened to int8, int32 accumulate, fp16 out",
             "data": "synthetic", "config": config,
             "tokens_per_s": M * n_gpus / (ms_step * 1e-3),
-            "gpu_launches": sum(1 if (L["khad"] == 0 and M <= 2) else 2 for L in work) * args.steps,
-            "launch_mode": "cuda_graph_replay" if graphs is not None else "eager",
+            "gpu_launches": res["launches_per_step"] * args.steps,
+            "launch_mode": res["launch_mode"],
             "roofline": roofline,
-            "quant_kernel": {"bound": "hbm", "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                             "frac": quant_gbs / peaks["hbm_gbs"], "ms_per_step": quant_ms_total},
-            "kernel_ms": per, "clocks": clocks}
+            "kernel_ms": {"kernel_b_all_linears": res["gemm_ms"], "kernel_a_all_linears": res["quant_ms"],
+                          "how": "each kernel family replayed alone as its own CUDA graph over the same buffers"},
+            "sustained": sustained, "clocks": clocks}
+    if res["quant_ms"]:
+        qbytes = sum(bytes_quant(M, K) for (_, K, _, _) in layers)
+        quant_gbs = qbytes / (res["quant_ms"] * 1e-3) / 1e9
+        line["quant_kernel"] = {"bound": "hbm", "achieved": quant_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                "frac": quant_gbs / peaks["hbm_gbs"], "ms_per_step": res["quant_ms"]}
 
     if not args.no_e2e:
-        e2e_ms, h2d, d2h = e2e_run(qb, layers, M, dev, max(3, min(args.steps, 10)), 6, work)
+        e2e_ms, h2d, d2h, h2d_ms, d2h_ms = e2e_run(qb, layers, M, dev, max(3, min(args.steps, 10)), 6, work)
         if dist is not None:
-            t = torch.tensor([e2e_ms], device=dev, dtype=torch.float64)
+            t = torch.tensor([e2e_ms, h2d_ms, d2h_ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            e2e_ms = float(t.item())
+            e2e_ms, h2d_ms, d2h_ms = (float(v) for v in t.tolist())
         line["e2e"] = {"value": total_ops / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS", "ms_per_step": e2e_ms,
                        "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                        "host_link_gbs": (h2d + d2h) / (e2e_ms * 1e-3) / 1e9,
+                       "h2d_alone_gbs_per_rank": h2d / (h2d_ms * 1e-3) / 1e9,
+                       "d2h_alone_gbs_per_rank": d2h / (d2h_ms * 1e-3) / 1e9,
                        "api": "torch.nn.Sequential(quarot_b200.nn.[Hadamard]Quantizer, quarot_b200.nn.Linear4bit) "
                               "with pinned host activations in and host fp16 results out"}
+    del res, work
+    torch.cuda.empty_cache()
+    if not args.no_others:
+        line["other_configs"] = other_configs(qb, dev, dist, world, rank, peaks, peak_src, args.workload, int8_probe)
+        if dist is not None:
+            line["parity"] = multi_gpu_parity(dev, world, rank, dist)
+        if _lib.kernel_status() != 0:
+            raise SystemExit("bench.py: a kernel reported a wait timeout in other_configs")
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         r = cpu_reference_run(layers, M, 2, 1, budget_s=12.0)
         line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}

@@ -53,9 +53,10 @@ const char* qr_last_error(void);
  * device.  No upstream counterpart (upstream never checks launches). */
 int qr_kernel_status(int* status_out);
 
-/* Kernel-selection knobs, process-wide: "gemm_bn", "gemm_pst", "gemm_grid", "gemm_swap_max_m", "gemm_splitk",
- * "gemm_2sm", "gemm_tma_out", "gemv_max_m", "pdl", "hadq_path", "hadq_tc".  Every setting computes the same
- * results; the defaults are the measured best choices.  Unknown keys return QR_EINVAL.  No upstream counterpart. */
+/* Kernel-selection knobs, process-wide: "gemm_bn", "gemm_bn2", "gemm_pst", "gemm_grid", "gemm_decode_max_m",
+ * "gemm_decode", "gemm_splitk", "gemm_2sm", "gemm_tma_out", "gemv_max_m", "pdl", "hadq_path", "hadq_tc",
+ * "hadq_walsh".  Every setting computes the same results; the defaults are the measured best choices.  Unknown keys
+ * return QR_EINVAL.  No upstream counterpart. */
 int qr_set_tuning(const char* key, int value);
 
 /* Self-test: the quantisers divide by the row scale with one multiplication by the rounded reciprocal.  This
@@ -181,15 +182,18 @@ int qr_quant_linear_i4_f16(const void* x, int64_t ldx, float clip, const uint8_t
                            const void* bias, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
                            void* stream);
 
-/* Decode-sized M (M <= 64) is bound by streaming the weights; with few output tiles a single pass
- * leaves most SMs idle, so the K loop of every tile can be split over several CTAs that meet in a
- * caller-provided scratch buffer (int32 partial tiles + one arrival counter per tile; the split that
- * arrives last reduces, nobody waits).  qr_linear_workspace_bytes returns the bytes needed for a
- * shape (0 when no split would be used).  The workspace must be 256-byte aligned device memory that
- * was zeroed once before its first use (the kernel leaves the counters at zero) and must not be
- * shared by launches that may overlap on the GPU.  Its first 64 KiB hold the arrival counters whatever the
- * shape and the partial tiles follow, so calls of different shapes may share one workspace.  Same result as qr_linear_i4_f16, bit for bit.
- * No upstream counterpart: upstream runs one CUTLASS GEMM without split-K (quarot/kernels/gemm.cu:16-41). */
+/* Decode-sized M (M <= 64) is bound by streaming the weights, so every SM has to stream its share.  Wide layers
+ * get there by dealing the weight rows out to the SMs, which needs no scratch.  A narrow layer (at most 48 weight rows
+ * per SM, e.g. N = 4096) would leave most of every 128-row MMA idle that way; its (128-row tile, k stage) units are
+ * dealt out instead, a tile may then be shared by several CTAs, and its pieces meet in a caller-provided scratch
+ * buffer: int32 partial sums added with integer atomics (exact, order independent) plus one arrival counter per
+ * tile; the piece that arrives last finishes the tile, nobody waits.  qr_linear_workspace_bytes returns the bytes
+ * needed for a shape (0 when the shape runs without scratch).  The workspace must be 256-byte aligned device memory
+ * that was zeroed once before its first use -- a kernel that ran to its end leaves what it used at zero; after a
+ * non-zero qr_kernel_status zero it again -- and must not be shared by launches that may overlap on the GPU.  Its
+ * first 64 KiB hold the arrival counters whatever the shape and the sums follow, so calls of different shapes may
+ * share one workspace.  Same result as qr_linear_i4_f16, bit for bit.
+ * No upstream counterpart: upstream runs one CUTLASS GEMM (quarot/kernels/gemm.cu:16-41). */
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
                         const void* bias, int64_t M, int64_t N, int64_t K,
@@ -200,20 +204,22 @@ int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, cons
  *
  * Who needs it: a host that gave all of its device memory to one arena at start-up (an inference
  * server with a fixed HBM budget, a framework whose caching allocator owns the rest of the card)
- * has nowhere to take the split-K workspace of qr_linear_i4_f16_ws from -- a late cudaMalloc can
+ * has nowhere to take the scratch buffer of qr_linear_i4_f16_ws from -- a late cudaMalloc can
  * fail there, and where it succeeds it synchronises the whole device in the middle of the decode
  * loop; a plain C caller in that loop may not own an allocator at all.  For them the scratch of the
- * decode kernel lives inside the library image: a fixed array of 4 MiB + 4 KiB in device memory, held by
+ * decode kernel lives inside the library image: a fixed array of 1 MiB + 64 KiB in device memory, held by
  * every GPU that loads the library until the process exits.
  *
  * Same arguments and the same result, bit for bit, as qr_linear_i4_f16.  The call allocates nothing
  * (no cudaMalloc / cudaFree, no allocating library routine).  Limits and rules:
- *   - shapes whose split-K scratch (qr_linear_workspace_bytes) exceeds that size are refused with
- *     QR_EUNSUPPORTED and a message; the LLaMA-2 7B and 70B decode shapes up to M = 64 fit;
+ *   - shapes whose scratch (qr_linear_workspace_bytes: 64 KiB of counters + 128 x BN x 4 bytes per tile of 128
+ *     output channels, BN = 16 / 32 / 64 for up to 16 / 32 / 64 token rows) exceeds that size are refused with
+ *     QR_EUNSUPPORTED and a message: N <= 4096 fits at every M <= 64, N <= 7104 at M <= 32; shapes that need no
+ *     scratch (wide layers, prefill sizes, a handful of rows) are simply run;
  *   - the first call on each device looks up the array's device address (once per device, with
  *     that device current); make that first call before any stream capture begins;
  *   - all calls share the one array and find the previous call's contents in it; the entry point
- *     clears the arrival counters it relies on at the start of every call, but two calls that may
+ *     clears the counters and sums it relies on at the start of every call (on the given stream), but two calls that may
  *     overlap on the GPU (different streams without an ordering between them) race on the array --
  *     order them, or give one of them its own workspace through qr_linear_i4_f16_ws. */
 int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,

@@ -61,8 +61,13 @@ def check(rc, what):
 
 
 def kernel_status():
+    """Device status word (0 = no kernel ever gave up on a bounded wait); reading clears it.  On a non-zero
+    status the cached scratch buffers are dropped, since the kernel may have left counters behind in them."""
     out = _int(0)
     check(lib.qr_kernel_status(ctypes.byref(out)), "qr_kernel_status")
+    if out.value != 0:
+        from . import _ops
+        _ops.reset_workspaces()
     return out.value
 
 

@@ -157,8 +157,15 @@ def hadamard_quant(x, had_k=None, K=0, clip=1.0, return_y=False, out_q=None, out
 _WORKSPACES = {}
 
 
+def reset_workspaces():
+    """Forget the cached scratch buffers.  A kernel that gave up on a bounded wait (non-zero
+    `_lib.kernel_status()`) may leave counters or sums behind in its scratch; fresh zeroed buffers are
+    allocated on the next use."""
+    _WORKSPACES.clear()
+
+
 def _workspace(dev, nbytes):
-    """Per-(device, stream) zero-initialised scratch for the split-K decode path, grown on demand.
+    """Per-(device, stream) zero-initialised scratch for narrow layers at decode sizes, grown on demand.
     Launches on one stream are ordered, so they can share it; different streams get their own."""
     key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
     ws = _WORKSPACES.get(key)
@@ -173,8 +180,8 @@ def linear_i4(q_x, scales_x, weight, weight_scales, bias=None, out=None, use_wor
 
     q_x uint8 [..., K/2], scales_x fp16 (any shape with one entry per row),
     weight uint8 [N, K/2], weight_scales fp16 [N] or [N, 1].  Returns fp16 [..., N].
-    For decode-sized inputs (at most 64 rows) the K loop is split over more CTAs through a cached
-    scratch buffer (`use_workspace=False` selects the single-pass kernel; results are identical).
+    For decode-sized inputs (at most 64 rows) on narrow layers the work is dealt out to all SMs through a
+    cached scratch buffer (`use_workspace=False` runs without scratch; results are identical).
     """
     assert q_x.shape[-1] % 32 == 0, "A.shape[-1]: {} must be multiplication of 32".format(q_x.shape[-1])
     assert scales_x.dtype == weight_scales.dtype == torch.float16

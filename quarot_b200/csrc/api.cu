@@ -88,11 +88,12 @@ int qr_kernel_status(int* status_out) {
 int qr_set_tuning(const char* key, int value) {
   static const struct { const char* name; int qr::Tuning::*field; } known[] = {
       {"gemm_bn", &qr::Tuning::gemm_bn},           {"gemm_pst", &qr::Tuning::gemm_pst},
-      {"gemm_grid", &qr::Tuning::gemm_grid},       {"gemm_swap_max_m", &qr::Tuning::gemm_swap_max_m},
+      {"gemm_grid", &qr::Tuning::gemm_grid},       {"gemm_decode_max_m", &qr::Tuning::gemm_decode_max_m},
       {"gemm_splitk", &qr::Tuning::gemm_splitk},   {"gemm_2sm", &qr::Tuning::gemm_2sm},
       {"gemm_tma_out", &qr::Tuning::gemm_tma_out}, {"gemv_max_m", &qr::Tuning::gemv_max_m},
       {"pdl", &qr::Tuning::pdl},                   {"hadq_path", &qr::Tuning::hadq_path},
-      {"hadq_tc", &qr::Tuning::hadq_tc},
+      {"hadq_tc", &qr::Tuning::hadq_tc},           {"gemm_decode", &qr::Tuning::gemm_decode},
+      {"gemm_bn2", &qr::Tuning::gemm_bn2},         {"hadq_walsh", &qr::Tuning::hadq_walsh},
   };
   if (!key) return qr::fail(QR_EINVAL, "qr_set_tuning: null key");
   for (const auto& k : known) {

@@ -20,18 +20,23 @@ int num_sms();
 // Kernel-selection knobs (qr_set_tuning); the defaults are the measured best choices.
 struct Tuning {
   int gemm_bn = 256;          // N tile of the 1-CTA GEMM (256, 128 or 64)
+  int gemm_bn2 = 0;           // N tile of the 2-CTA GEMM: 0 = chosen per shape, else 256, 240, 224 or 192
   int gemm_pst = 4;           // packed staging slots of the 1-CTA GEMM at BN = 256 (4 or 3)
   int gemm_grid = 0;          // cap on the number of persistent CTAs / clusters (0 = one per SM / SM pair)
-  int gemm_swap_max_m = 64;   // token rows up to which the weights take the MMA rows (decode)
-  int gemm_splitk = 1;        // decode: split the K loop over several CTAs when a workspace is given
+  int gemm_decode_max_m = 64; // token rows up to which the weight-streaming kernels are used (decode)
+  int gemm_splitk = 1;        // decode, narrow layers: deal out (tile, stage) units when a workspace is given
   int gemm_2sm = 1;           // prefill: 2-CTA kernel (cta_group::2) instead of the 1-CTA kernel
   int gemm_tma_out = 1;       // 2-CTA kernel: tiled TMA stores of the output where alignment allows
-  int gemv_max_m = 8;         // token rows up to which the weight-streaming CUDA-core kernel is used
-  int pdl = 0;                // launch the kernels with programmatic stream serialization
+  int gemv_max_m = 4;         // token rows up to which the weight-streaming CUDA-core kernel is used
+  int gemm_decode = 1;        // decode: the weight-streaming tcgen05 kernel (0: tokens on the MMA rows as at prefill)
+  int pdl = 2;                // programmatic dependent launch: 0 never, 1 always, 2 decode-sized launches only
   int hadq_path = 0;          // 1 = always the generic Hadamard kernel (A/B checks)
+  int hadq_walsh = 1;         // warp-per-row register kernel for Walsh lengths 256 .. 4096
   int hadq_tc = 1;            // tensor-core kernel for n = 64 K Kronecker shapes
 };
 extern Tuning g_tuning;
+// programmatic dependent launch for a launch that works on `rows` token rows?
+static inline bool use_pdl(int64_t rows) { return g_tuning.pdl == 1 || (g_tuning.pdl == 2 && rows <= 64); }
 
 #define QR_CUDA(expr)                                            \
   do {                                                           \

@@ -25,9 +25,8 @@
 // double-buffers the accumulator so the epilogue of tile i overlaps the main loop
 // of tile i+1.
 //
-// SWAP = true serves decode-sized M: the weights become operand P (filling the 128
-// MMA rows) and the few token rows become operand Q (BN = 16..64); the epilogue then
-// writes the transposed tile.
+// Decode-sized M (at most 64 token rows) is served by gemm_i4_decode.cu (weights on the MMA rows,
+// all SMs streaming) and, for a handful of rows, by gemv_i4.cu.
 //
 // Every mbarrier wait is bounded: after about two seconds of polling the waiting thread
 // raises a CTA-wide abort flag and the device status word, every role leaves its
@@ -52,11 +51,9 @@ struct GemmParams {
   const __half* sP;      // per-row scale of operand P (fp16) or null (MODE_I32)
   const __half* sQ;
   const __half* bias;    // per output channel or null
-  int splits;            // 1-CTA kernel: k splits per tile (1 = none); > 1 needs the scratch buffers below
-  int32_t* ws_partial;   // [tiles][splits][BN][128] int32 partial tiles
-  int* ws_counter;       // [tiles] arrival counters, zero before and after every launch
   int vec_ok;            // output rows, scales and bias are 16-byte aligned: vector epilogue allowed
   int swiglu;            // 2-CTA kernel, fp16 mode: columns [0,128) / [128,256) of a tile are gate / up channels; out = silu(gate) * up
+  int bn;                // 2-CTA kernel: N of the pair tile (a multiple of 16, at most 256); 256 unless fp16 mode with one output
   int n_outs;            // 2-CTA kernel: number of output matrices that receive the result (1, or one per GPU of a column split)
   int tma_out;           // 2-CTA kernel: the output has a tensor map (16-byte aligned base and row pitch): tiled stores
   int* status;
@@ -82,7 +79,7 @@ struct SmemLayout {
   static constexpr int kDynamic = kTotal + 1024;  // slack for manual 1024-byte alignment
 };
 
-template <int BN, int PST, int IST, int ACC, bool SWAP, int MODE>
+template <int BN, int PST, int IST, int ACC, int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ, const GemmParams p) {
   using L = SmemLayout<BN, PST, IST>;
@@ -103,7 +100,6 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   auto acc_empty = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + 2 + a); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
-  volatile int* last_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff + 4);
 
   constexpr uint32_t kTmemCols = (ACC * BN) < 32 ? 32 : (ACC * BN);
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
@@ -128,13 +124,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // A work item is (tile, k split): split sp of a tile covers k-blocks [kb0, kb1).  With splits == 1 this
-  // is the plain tile loop; with splits > 1 (decode-sized M) partial tiles meet in a scratch buffer.
-  const int splits = p.splits;
-  const int num_tiles = p.tilesP * p.tilesQ * splits;
-  const int num_kb_all = (p.K + 127) >> 7;
-  auto kb_begin = [&](int w) { return (int)(((long long)(w % splits) * num_kb_all) / splits); };
-  auto kb_end = [&](int w) { return (int)(((long long)(w % splits + 1) * num_kb_all) / splits); };
+  const int num_tiles = p.tilesP * p.tilesQ;
+  const int num_kb = (p.K + 127) >> 7;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -142,10 +133,9 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
       pdl_wait();   // operands may come from the preceding kernel
       uint32_t it = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
-        const int tile = w / splits;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int tp = tile % p.tilesP, tq = tile / p.tilesP;
-        for (int kb = kb_begin(w); kb < kb_end(w); ++kb, ++it) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % PST;
           const uint32_t ph = (it / PST) & 1;
           if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
@@ -162,14 +152,13 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
       constexpr uint32_t idesc = make_idesc_i8(kBM, BN);
       uint32_t it = 0, tl = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tl) {
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
         const int a = tl % ACC;
         const uint32_t pha = (tl / ACC) & 1;
         if (!mbar_wait(acc_empty(a), pha ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
-        const int kb0 = kb_begin(w);
-        for (int kb = kb0; kb < kb_end(w); ++kb, ++it) {
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % IST;
           const uint32_t ph = (it / IST) & 1;
           if (!mbar_wait(full_i(s), ph, abort_flag, p.status, 3)) { ok = false; break; }
@@ -180,7 +169,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             // +32 bytes along K inside the swizzle atom = +2 in the (addr >> 4) field
-            umma_i8(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb != kb0 || k4 != 0) ? 1u : 0u);
+            umma_i8(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb != 0 || k4 != 0) ? 1u : 0u);
           }
           umma_commit(empty_i(s));
         }
@@ -188,14 +177,13 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
       }
     }
   } else if (warp < 2 + kEpiWarps) {
-    // ------------------------------------------------------------ epilogue
+    // ------------------------------------------------------------ epilogue: thread = one output row (a token)
     const int q4 = warp & 3;                 // TMEM lane quarter this warp may access
     const int prow_in_tile = q4 * 32 + lane; // accumulator row owned by this thread
-    pdl_wait();   // scales, output and scratch are touched only after the preceding kernel has finished
+    pdl_wait();   // scales and output are touched only after the preceding kernel has finished
     uint32_t tl = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x, ++tl) {
-      const int tile = w / splits, sp_idx = w % splits;
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tl) {
       const int tp = tile % p.tilesP, tq = tile / p.tilesP;
       const int a = tl % ACC;
       const uint32_t pha = (tl / ACC) & 1;
@@ -219,126 +207,56 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
           if (lane == 0) mbar_arrive(acc_empty(a));
         }
         const int qcol0 = tq * BN + c0;
-        if (splits > 1) {
-          // partial tile -> scratch, column-major so that the 32 lanes of a warp store 128 contiguous bytes
-          int32_t* part = p.ws_partial + ((size_t)(tile * splits + sp_idx) * BN + c0) * kBM + prow_in_tile;
+        if (!prow_ok) continue;
+        if (MODE == MODE_I32) {
+          int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
+          if (qcol0 + CH <= p.rowsQ && p.vec_ok) {
 #pragma unroll
-          for (int j = 0; j < CH; ++j) part[(size_t)j * kBM] = (int32_t)r[j] >> 8;
-          continue;
-        }
-        if (!SWAP) {
-          // thread owns output row `prow` (a token), columns qcol0.. (output channels)
-          if (prow_ok) {
-            if (MODE == MODE_I32) {
-              int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-              if (qcol0 + CH <= p.rowsQ && p.vec_ok) {
+            for (int j = 0; j < CH; j += 4)
+              *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
+                                                          (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
+          } else {
 #pragma unroll
-                for (int j = 0; j < CH; j += 4)
-                  *reinterpret_cast<int4*>(o + j) = make_int4((int32_t)r[j] >> 8, (int32_t)r[j + 1] >> 8,
-                                                              (int32_t)r[j + 2] >> 8, (int32_t)r[j + 3] >> 8);
-              } else {
-#pragma unroll
-                for (int j = 0; j < CH; ++j)
-                  if (qcol0 + j < p.rowsQ) o[j] = (int32_t)r[j] >> 8;
-              }
-            } else {
-              __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
-              const bool full = (qcol0 + CH <= p.rowsQ) && p.vec_ok;
-              if (full) {
-#pragma unroll
-                for (int j = 0; j < CH; j += 8) {
-                  uint4 pk;
-                  __half2* h = reinterpret_cast<__half2*>(&pk);
-                  const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + j));
-                  const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 sc = __half22float2(sqh[e]);
-                    const float v0 = (float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x);
-                    const float v1 = (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y);
-                    h[e] = __floats2half2_rn(v0, v1);
-                  }
-                  if (p.bias) {
-                    const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + j));
-                    const __half2* bh = reinterpret_cast<const __half2*>(&bb);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
-                  }
-                  *reinterpret_cast<uint4*>(o + j) = pk;
-                }
-              } else {
-#pragma unroll
-                for (int j = 0; j < CH; ++j) {
-                  if (qcol0 + j < p.rowsQ) {
-                    const float sc = __half2float(p.sQ[qcol0 + j]);
-                    __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sp * sc));
-                    if (p.bias) v = __hadd(v, p.bias[qcol0 + j]);
-                    o[j] = v;
-                  }
-                }
-              }
-            }
+            for (int j = 0; j < CH; ++j)
+              if (qcol0 + j < p.rowsQ) o[j] = (int32_t)r[j] >> 8;
           }
         } else {
-          // SWAP: thread owns output channel `prow`; columns are token rows qcol0..
-          if (prow_ok) {
+          __half* o = reinterpret_cast<__half*>(p.out) + (int64_t)prow * p.ldo + qcol0;
+          const bool full = (qcol0 + CH <= p.rowsQ) && p.vec_ok;
+          if (full) {
+#pragma unroll
+            for (int j = 0; j < CH; j += 8) {
+              uint4 pk;
+              __half2* h = reinterpret_cast<__half2*>(&pk);
+              const uint4 sq = __ldg(reinterpret_cast<const uint4*>(p.sQ + qcol0 + j));
+              const __half2* sqh = reinterpret_cast<const __half2*>(&sq);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float2 sc = __half22float2(sqh[e]);
+                const float v0 = (float)((int32_t)r[j + 2 * e] >> 8) * (sp * sc.x);
+                const float v1 = (float)((int32_t)r[j + 2 * e + 1] >> 8) * (sp * sc.y);
+                h[e] = __floats2half2_rn(v0, v1);
+              }
+              if (p.bias) {
+                const uint4 bb = __ldg(reinterpret_cast<const uint4*>(p.bias + qcol0 + j));
+                const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], bh[e]);
+              }
+              *reinterpret_cast<uint4*>(o + j) = pk;
+            }
+          } else {
 #pragma unroll
             for (int j = 0; j < CH; ++j) {
-              const int tok = qcol0 + j;
-              if (tok < p.rowsQ) {
-                if (MODE == MODE_I32) {
-                  reinterpret_cast<int32_t*>(p.out)[(int64_t)tok * p.ldo + prow] = (int32_t)r[j] >> 8;
-                } else {
-                  const float sc = __half2float(__ldg(p.sQ + tok));
-                  __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sc * sp));
-                  if (p.bias) v = __hadd(v, p.bias[prow]);
-                  reinterpret_cast<__half*>(p.out)[(int64_t)tok * p.ldo + prow] = v;
-                }
+              if (qcol0 + j < p.rowsQ) {
+                const float sc = __half2float(p.sQ[qcol0 + j]);
+                __half v = __float2half_rn((float)((int32_t)r[j] >> 8) * (sp * sc));
+                if (p.bias) v = __hadd(v, p.bias[qcol0 + j]);
+                o[j] = v;
               }
             }
           }
         }
-      }
-      if (splits > 1) {
-        // The split that arrives last at the tile's counter adds up all partial tiles and writes the output;
-        // nobody waits for anybody.  The counter is left at zero for the next launch.
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"r"(32 * kEpiWarps) : "memory");
-        if (threadIdx.x == 32 * 2) *last_flag = (atomicAdd(p.ws_counter + tile, 1) == splits - 1) ? 1 : 0;
-        asm volatile("bar.sync 1, %0;" ::"r"(32 * kEpiWarps) : "memory");
-        if (*last_flag) {
-          __threadfence();
-          if (prow_ok) {
-            for (int j = 0; j < BN; ++j) {
-              const int col = tq * BN + j;
-              if (col >= p.rowsQ) break;
-              int32_t acc = 0;
-              for (int s2 = 0; s2 < splits; ++s2)
-                acc += __ldcg(p.ws_partial + ((size_t)(tile * splits + s2) * BN + j) * kBM + prow_in_tile);
-              if (SWAP) {
-                if (MODE == MODE_I32) {
-                  reinterpret_cast<int32_t*>(p.out)[(int64_t)col * p.ldo + prow] = acc;
-                } else {
-                  const float sc = __half2float(__ldg(p.sQ + col));
-                  __half v = __float2half_rn((float)acc * (sc * sp));
-                  if (p.bias) v = __hadd(v, p.bias[prow]);
-                  reinterpret_cast<__half*>(p.out)[(int64_t)col * p.ldo + prow] = v;
-                }
-              } else {
-                if (MODE == MODE_I32) {
-                  reinterpret_cast<int32_t*>(p.out)[(int64_t)prow * p.ldo + col] = acc;
-                } else {
-                  const float sc = __half2float(__ldg(p.sQ + col));
-                  __half v = __float2half_rn((float)acc * (sp * sc));
-                  if (p.bias) v = __hadd(v, p.bias[col]);
-                  reinterpret_cast<__half*>(p.out)[(int64_t)prow * p.ldo + col] = v;
-                }
-              }
-            }
-          }
-          if (threadIdx.x == 32 * 2) p.ws_counter[tile] = 0;
-        }
-        asm volatile("bar.sync 1, %0;" ::"r"(32 * kEpiWarps) : "memory");
       }
     }
   } else {
@@ -350,8 +268,8 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
     const int wt = wt_all - group * kWThreads;
     uint32_t it = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_tiles && ok; w += gridDim.x) {
-      for (int kb = kb_begin(w); kb < kb_end(w); ++kb, ++it) {
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((int)(it % kGroups) != group) continue;
         const int sp_ = it % PST, si = it % IST;
         const uint32_t php = (it / PST) & 1, phi = (it / IST) & 1;
@@ -408,7 +326,7 @@ gemm_i4_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ 
 //   acc_empty (leader) <- 4 local + 4 remote epilogue-warp arrivals
 // TMA loads are CTA-local (no multicast of data); the MMA-completion signal is one commit
 // delivered to the same barrier in both CTAs.
-constexpr int kBN2 = 256;            // N of the pair tile; each CTA holds kBN2 / 2 rows of operand Q
+constexpr int kBN2 = 256;            // largest N of the pair tile (GemmParams::bn is the one in use); each CTA holds bn / 2 rows of operand Q
 constexpr int kMaxOuts = 8;          // output matrices one launch can write (the GPUs of a column split)
 struct OutMaps { CUtensorMap m[kMaxOuts]; };
 constexpr int kRows2 = kBM + kBN2 / 2;  // operand rows per CTA per stage (128 P + 128 Q)
@@ -452,10 +370,46 @@ __device__ __forceinline__ int widen_index2(int w) {
   return w - 5 - ((w - 5) >> 2);   // 6,7,8 -> 1,2,3; 10,11,12 -> 4,5,6; 14,15,16 -> 7,8,9; 18,19 -> 10,11
 }
 
-template <int PST, int IST, int MODE>
+// fp16 epilogue of 16 accumulator columns (tile widths that are not a multiple of 64): dequantise, stage as 32 rows x 32
+// bytes and hand the piece to the TMA unit.  Kept out of line so that it does not add to the register count of the
+// kernel's hot loops.
+__device__ __noinline__ void store_tail_piece(uint32_t taddr, const float* sq, const __half* bias, float sp, unsigned char* stg,
+                                              uint32_t stg_u32, int lane, const CUtensorMap* map, int x, int y, bool in_range) {
+  uint32_t r[32];
+  tmem_ld16(taddr, r);
+  uint4 pk[2];
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+    __half2* hh = reinterpret_cast<__half2*>(&pk[e]);
+    const float4 s0 = *reinterpret_cast<const float4*>(sq + 8 * e);
+    const float4 s1 = *reinterpret_cast<const float4*>(sq + 8 * e + 4);
+    hh[0] = __floats2half2_rn((float)(int32_t)r[8 * e + 0] * (sp * s0.x), (float)(int32_t)r[8 * e + 1] * (sp * s0.y));
+    hh[1] = __floats2half2_rn((float)(int32_t)r[8 * e + 2] * (sp * s0.z), (float)(int32_t)r[8 * e + 3] * (sp * s0.w));
+    hh[2] = __floats2half2_rn((float)(int32_t)r[8 * e + 4] * (sp * s1.x), (float)(int32_t)r[8 * e + 5] * (sp * s1.y));
+    hh[3] = __floats2half2_rn((float)(int32_t)r[8 * e + 6] * (sp * s1.z), (float)(int32_t)r[8 * e + 7] * (sp * s1.w));
+    if (bias) {
+      const uint4 bb = *reinterpret_cast<const uint4*>(bias + 8 * e);
+      const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) hh[q] = __hadd2(hh[q], bh[q]);
+    }
+  }
+  if (lane == 0) bulk_wait_read_all();   // the TMA unit has read the previous block out of the staging area
+  __syncwarp();
+  *reinterpret_cast<uint4*>(stg + lane * 32) = pk[0];
+  *reinterpret_cast<uint4*>(stg + lane * 32 + 16) = pk[1];
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && in_range) {
+    tma_store_2d(map, stg_u32, x, y);
+    bulk_commit_group();
+  }
+}
+
+template <int PST, int IST, int MODE, int BN2>
 __global__ void __launch_bounds__(kThreads2, 1)
 gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constant__ CUtensorMap tmQ,
-                   const __grid_constant__ OutMaps tmOs, const GemmParams p) {
+                   const __grid_constant__ OutMaps tmOs, const __grid_constant__ CUtensorMap tmTail, const GemmParams p) {
   using L = SmemLayout2<PST, IST>;
   constexpr int ACC = 2;
   extern __shared__ unsigned char smem_dyn[];
@@ -504,6 +458,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_tiles = p.tilesP * p.tilesQ;     // pair tiles
+  constexpr int bn = BN2;                         // columns of a pair tile; bn / 2 rows of operand Q per CTA
+  static_assert(BN2 % 16 == 0 && BN2 >= 128 && BN2 <= kBN2, "pair tile width");
   const int num_kb = (p.K + 127) >> 7;
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
@@ -520,10 +476,10 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           const int s = it % PST;
           const uint32_t ph = (it / PST) & 1;
           if (!mbar_wait(empty_p(s), ph ^ 1, abort_flag, p.status, 11)) { ok = false; break; }
-          mbar_expect_tx(full_p(s), L::kPkStage);
+          mbar_expect_tx(full_p(s), (uint32_t)((kBM + (bn >> 1)) * kBKBytes));
           const uint32_t dst = smem_base + L::kPkOff + s * L::kPkStage;
           tma_load_2d(dst, &tmP, full_p(s), kb * kBKBytes, tp * 2 * kBM + (int)rank * kBM);
-          tma_load_2d(dst + kBM * kBKBytes, &tmQ, full_p(s), kb * kBKBytes, tq * kBN2 + (int)rank * (kBN2 / 2));
+          tma_load_2d(dst + kBM * kBKBytes, &tmQ, full_p(s), kb * kBKBytes, tq * bn + (int)rank * (bn >> 1));
         }
       }
     }
@@ -537,7 +493,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     // the next block and its commit while the other thread issues.
     if (leader && lane == 0) {
       const int me = (warp == kIssuerAWarp) ? 0 : 1;
-      constexpr uint32_t idesc = make_idesc_i8(2 * kBM, kBN2);
+      constexpr uint32_t idesc = make_idesc_i8(2 * kBM, bn);
       const uint32_t peer_acc_full0 = mapa_cluster(acc_full(0), 1);
       uint32_t it = 0, tl = 0;
       bool ok = true;
@@ -623,8 +579,8 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
       if (MODE == MODE_F16 && p.tma_out) {
         __syncwarp();   // the previous tile's reads of the scale block are done
 #pragma unroll
-        for (int j = lane; j < kBN2; j += 32) {
-          const int col = tq * kBN2 + j;
+        for (int j = lane; j < bn; j += 32) {
+          const int col = tq * bn + j;
           sqf[j] = col < p.rowsQ ? __half2float(p.sQ[col]) * 0.00390625f : 0.0f;   // 1/256: the accumulator is 256 x the dot product
           if (p.bias) bsh[j] = col < p.rowsQ ? p.bias[col] : __float2half(0.0f);
         }
@@ -695,14 +651,15 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
       } else if (p.tma_out) {
         const int row0 = tp * 2 * kBM + (int)rank * kBM + q4 * 32;
+        constexpr int full_cols = (MODE == MODE_I32) ? bn : (bn & ~63);    // fp16: whole 64-column blocks, then 16-column pieces
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN2; c0 += CW) {
+        for (int c0 = 0; c0 < full_cols; c0 += CW) {
 #pragma unroll
           for (int h = 0; h < CW / 32; ++h) {
             uint32_t r[32];
             tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0 + 32 * h), r);
             tmem_ld_wait();
-            if (c0 + CW >= kBN2 && h == CW / 32 - 1) release_acc();
+            if (c0 + CW >= bn && h == CW / 32 - 1) release_acc();
             if (MODE == MODE_I32) {
               if (lane == 0) bulk_wait_read_all();   // the TMA unit has read the previous block out of the staging area
               __syncwarp();
@@ -746,22 +703,33 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && row0 < p.rowsP && tq * kBN2 + c0 < p.rowsQ) {
+          if (lane == 0 && row0 < p.rowsP && tq * bn + c0 < p.rowsQ) {
             // one tiled store per destination: the block goes to this GPU's output and, in a column split, straight
             // into the peers' copies of the full matrix over NVLink
-            for (int g = 0; g < p.n_outs; ++g) tma_store_2d(&tmOs.m[g], stg_u32, tq * kBN2 + c0, row0);
+            for (int g = 0; g < p.n_outs; ++g) tma_store_2d(&tmOs.m[g], stg_u32, tq * bn + c0, row0);
             bulk_commit_group();
+          }
+        }
+        if (MODE == MODE_F16 && (bn & 63) != 0) {
+          // tile widths that are not a multiple of 64 (chosen so that the tiles fill whole waves of clusters): the
+          // remaining columns leave as 16-column pieces through a second tensor map (32 rows x 32 bytes, unswizzled)
+#pragma unroll 1
+          for (int c0 = full_cols; c0 < bn; c0 += 16) {
+            store_tail_piece(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0), sqf + c0,
+                             p.bias ? bsh + c0 : nullptr, sp, stg, stg_u32, lane, &tmTail, tq * bn + c0, row0,
+                             row0 < p.rowsP && tq * bn + c0 < p.rowsQ);
+            if (c0 + 16 >= bn) release_acc();
           }
         }
       } else {
         // output without a tensor map (unaligned base or row pitch): element-wise stores
 #pragma unroll 1
-        for (int c0 = 0; c0 < kBN2; c0 += 32) {
+        for (int c0 = 0; c0 < bn; c0 += 32) {      // bn is 256 on this path
           uint32_t r[32];
           tmem_ld32(tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2 + c0), r);
           tmem_ld_wait();
-          if (c0 + 32 >= kBN2) release_acc();
-          const int qcol0 = tq * kBN2 + c0;
+          if (c0 + 32 >= bn) release_acc();
+          const int qcol0 = tq * bn + c0;
           if (prow_ok) {
             if (MODE == MODE_I32) {
               int32_t* o = reinterpret_cast<int32_t*>(p.out) + (int64_t)prow * p.ldo + qcol0;
@@ -793,9 +761,9 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     const int wi = widen_index2(warp);
     const int group = wi / kWidenWarpsPerGroup2;                               // three warps per group
     const int gt = (wi % kWidenWarpsPerGroup2) * 32 + lane;                    // 0 .. 95 inside the group
-    constexpr int kChunks = kRows2 * 4;                 // 1024 packed 16-byte chunks per stage
+    constexpr int kChunks = (kBM + (bn >> 1)) * 4;      // packed 16-byte chunks per stage (1024 at bn = 256)
     constexpr int kGThreads = 32 * kWidenWarpsPerGroup2;
-    constexpr int kPer = (kChunks + kGThreads - 1) / kGThreads;   // 11 chunks per thread (the last round is partial)
+    constexpr int kPer = (kChunks + kGThreads - 1) / kGThreads;   // 11 chunks per thread at bn = 256 (the last round is partial)
     const uint32_t leader_full_i0 = mapa_cluster(full_i(0), 0);
     uint32_t it = 0;
     bool ok = true;
@@ -908,26 +876,27 @@ static int make_packed_map(CUtensorMap* map, const void* base, int64_t rows, int
 
 // Tensor map over the output matrix [rows, cols] with a row pitch of ldo elements (fp16 or int32), box = 128 bytes
 // of a row x 32 rows, 128-byte swizzle: what one epilogue warp of the 2-CTA kernel stores at a time.
-static int make_out_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldo, bool is_i32) {
+// (tail = true: 16 fp16 columns x 32 rows, unswizzled, for tile widths that are not a multiple of 64.)
+static int make_out_map(CUtensorMap* map, void* base, int64_t rows, int64_t cols, int64_t ldo, bool is_i32, bool tail = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) return fail(QR_ENOTREADY, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t esz = is_i32 ? 4 : 2;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ldo * esz};
-  cuuint32_t box[2] = {(cuuint32_t)(128 / esz), 32};
+  cuuint32_t box[2] = {(cuuint32_t)(tail ? 16 : 128 / esz), 32};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, is_i32 ? CU_TENSOR_MAP_DATA_TYPE_INT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides,
-                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, tail ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B,
                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(QR_EINVAL, "cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
   return QR_OK;
 }
 
-template <int BN, int PST, int IST, int ACC, bool SWAP, int MODE>
+template <int BN, int PST, int IST, int ACC, int MODE>
 static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const GemmParams& p, int grid_cap, cudaStream_t st) {
   using L = SmemLayout<BN, PST, IST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
-  auto kern = gemm_i4_kernel<BN, PST, IST, ACC, SWAP, MODE>;
+  auto kern = gemm_i4_kernel<BN, PST, IST, ACC, MODE>;
   static thread_local bool configured[64] = {false};
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
@@ -935,10 +904,10 @@ static int launch_gemm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const Gem
     QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kDynamic));
     if (dev < 64) configured[dev] = true;
   }
-  int grid = p.tilesP * p.tilesQ * p.splits;
+  int grid = p.tilesP * p.tilesQ;
   int cap = grid_cap > 0 ? grid_cap : num_sms();
   if (grid > cap) grid = cap;
-  QR_CUDA(launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)L::kDynamic, st, g_tuning.pdl != 0, tmP, tmQ, p));
+  QR_CUDA(launch_kernel(kern, dim3(grid), dim3(kThreads), (size_t)L::kDynamic, st, use_pdl(p.rowsP), tmP, tmQ, p));
   return QR_OK;
 }
 
@@ -946,15 +915,29 @@ template <typename Kern, typename... Maps>
 static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clusters, const GemmParams& p, int grid_cap,
                            cudaStream_t st, bool pdl, const Maps&... maps);
 
-template <int PST, int IST, int MODE>
-static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const OutMaps& tmO, const GemmParams& p,
-                           int grid_cap, cudaStream_t st) {
+template <int PST, int IST, int MODE, int BN2>
+static int launch_gemm_2sm_bn(const CUtensorMap& tmP, const CUtensorMap& tmQ, const OutMaps& tmO, const CUtensorMap& tmTail,
+                              const GemmParams& p, int grid_cap, cudaStream_t st) {
   using L = SmemLayout2<PST, IST>;
   static_assert(L::kDynamic <= 227 * 1024, "shared memory budget exceeded");
   static_assert(L::kStageOff % 1024 == 0, "staging blocks must be 1024-byte aligned for the 128-byte swizzle");
   static thread_local int max_clusters[64] = {0};
-  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE>, kThreads2, L::kDynamic, max_clusters, p, grid_cap, st,
-                         g_tuning.pdl != 0, tmP, tmQ, tmO);
+  return launch_cluster2(gemm_i4_2sm_kernel<PST, IST, MODE, BN2>, kThreads2, L::kDynamic, max_clusters, p, grid_cap, st,
+                         use_pdl(p.rowsP), tmP, tmQ, tmO, tmTail);
+}
+
+// pair-tile widths the fp16 epilogue is compiled for (the int32 path always uses 256)
+constexpr int kPairWidths[] = {256, 240, 224, 192};
+
+template <int PST, int IST, int MODE>
+static int launch_gemm_2sm(const CUtensorMap& tmP, const CUtensorMap& tmQ, const OutMaps& tmO, const CUtensorMap& tmTail,
+                           const GemmParams& p, int grid_cap, cudaStream_t st) {
+  if (MODE == MODE_F16) {
+    if (p.bn == 240) return launch_gemm_2sm_bn<PST, IST, MODE_F16, 240>(tmP, tmQ, tmO, tmTail, p, grid_cap, st);
+    if (p.bn == 224) return launch_gemm_2sm_bn<PST, IST, MODE_F16, 224>(tmP, tmQ, tmO, tmTail, p, grid_cap, st);
+    if (p.bn == 192) return launch_gemm_2sm_bn<PST, IST, MODE_F16, 192>(tmP, tmQ, tmO, tmTail, p, grid_cap, st);
+  }
+  return launch_gemm_2sm_bn<PST, IST, MODE, kBN2>(tmP, tmQ, tmO, tmTail, p, grid_cap, st);
 }
 
 template <typename Kern, typename... Maps>
@@ -992,36 +975,12 @@ static int launch_cluster2(Kern kern, int threads, int smem_bytes, int* max_clus
   return QR_OK;
 }
 
-// Number of k splits the decode path would use for (M, N, K) and the scratch bytes that needs
-// (arrival counters, padded to 256 bytes, followed by the int32 partial tiles).
-//  The rule: split only when the tiles alone leave SMs idle, as many ways as whole copies of the tile set fit on the
-//  SMs.  With a caller-provided workspace (measured = true) the rule is switched off where it was measured to lose:
-//  for more than 32 token rows the partial-tile epilogue (32 KB per item, re-read by the last arriver) costs more
-//  than the idle SMs (7B decode layer at M = 64: 147 us with splits, 134 us without).  Splitting further, so that
-//  the persistent CTAs take several (tile, split) items each, was measured too and loses badly (M = 32: 113 -> 235 us).
-static int decode_splits(int64_t M, int64_t N, int64_t K, size_t* bytes, size_t* counter_bytes = nullptr, bool measured = false) {
-  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-  const int tiles = (int)((N + kBM - 1) / kBM) * (int)((M + bn - 1) / bn);
-  const int num_kb = (int)((K + 127) / 128);
-  const int sms = num_sms();
-  int splits = sms / (tiles > 0 ? tiles : 1);
-  if (splits > 8) splits = 8;
-  if (splits > num_kb / 4) splits = num_kb / 4;
-  if (splits < 1) splits = 1;
-  if (measured && M > 32) splits = 1;
-  if (bytes) *bytes = splits > 1 ? (((size_t)tiles * 4 + 255) & ~(size_t)255) + (size_t)tiles * splits * bn * kBM * 4 : 0;
-  if (counter_bytes) *counter_bytes = ((size_t)tiles * 4 + 255) & ~(size_t)255;
-  return splits;
-}
-
-
-// A caller-provided workspace starts with a counter region of fixed size, whatever the shape: the kernels leave
-// their counters at zero, so calls of different shapes can share one workspace without the partial tiles of one
-// shape ever landing where another shape keeps its counters.  (The library's built-in scratch uses a compact
-// layout and is cleared before every call instead.)
-constexpr size_t kWsCounterRegion = 64u << 10;
-
-// weight-streaming kernel for M <= 8 (gemv_i4.cu)
+// weight-streaming tcgen05 kernel for M <= 64 (gemm_i4_decode.cu)
+int launch_gemm_i4_decode(const uint8_t* X, const uint8_t* W, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                          const void* sX, const void* sW, const void* bias, bool f16, int grid_cap, void* ws, size_t ws_bytes,
+                          cudaStream_t st);
+size_t decode_stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
+// weight-streaming CUDA-core kernel for M <= 8 (gemv_i4.cu)
 int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
                    const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st,
                    const void* x = nullptr, int64_t ldx = 0, float clip = 1.0f);
@@ -1029,7 +988,7 @@ int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int
 template <int MODE>
 static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K,
                     void* out, int64_t ldo, const void* sA, const void* sB, const void* bias, cudaStream_t st,
-                    void* ws = nullptr, size_t ws_bytes = 0, bool compact_ws = false,
+                    void* ws = nullptr, size_t ws_bytes = 0,
                     void* const* more_outs = nullptr, int n_more = 0, bool swiglu = false) {
   if (M < 0 || N < 0 || K < 0) return fail(QR_EINVAL, "%s: negative size", who);
   if (M == 0 || N == 0) return QR_OK;
@@ -1043,43 +1002,59 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   int* status = kernel_status_ptr();
   if (!status) return fail(QR_ENOTREADY, "%s: no CUDA device", who);
 
-  const int swap_max_m = g_tuning.gemm_swap_max_m;
-  const bool swap = M <= swap_max_m;
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
-  p.splits = 1; p.ws_partial = nullptr; p.ws_counter = nullptr;
   p.bias = reinterpret_cast<const __half*>(bias);
-  p.tma_out = 0; p.n_outs = 1; p.swiglu = 0;
+  p.tma_out = 0; p.n_outs = 1; p.swiglu = 0; p.bn = kBN2;
   if (swiglu) {
-    if (swap || M <= kBM || g_tuning.gemm_2sm == 0)
+    if (M <= kBM || g_tuning.gemm_2sm == 0)
       return fail(QR_EUNSUPPORTED, "%s: served by the prefill kernel only (more than %d rows)", who, kBM);
     if (N % kBN2 != 0) return fail(QR_EINVAL, "%s: N = %lld must be a multiple of %d (interleaved gate/up rows)", who, (long long)N, kBN2);
     if (bias) return fail(QR_EUNSUPPORTED, "%s: bias is not supported", who);
     if (!aligned16(out) || ldo % 8 != 0) return fail(QR_EALIGN, "%s: output must be 16-byte aligned with ldo %% 8 == 0", who);
     if (ldo < N / 2) return fail(QR_EINVAL, "%s: ldo < N / 2", who);
   }
-  if (n_more > 0 && (swap || M <= kBM || g_tuning.gemm_2sm == 0))
+  if (n_more > 0 && (M <= kBM || g_tuning.gemm_2sm == 0))
     return fail(QR_EUNSUPPORTED, "%s: several outputs are served by the prefill kernel only (more than %d rows)", who, kBM);
   p.vec_ok = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) &&
              (MODE == MODE_I32 || (aligned16(sB) && (!bias || aligned16(bias))));
   CUtensorMap tmP, tmQ;
   int rc;
   const int grid_cap = g_tuning.gemm_grid;
-  if (!swap && M > kBM && g_tuning.gemm_2sm != 0) {
+  if (M > kBM && g_tuning.gemm_2sm != 0) {
     p.rowsP = (int)M; p.rowsQ = (int)N;
-    p.tilesP = (int)((M + 2 * kBM - 1) / (2 * kBM)); p.tilesQ = (int)((N + kBN2 - 1) / kBN2);
+    p.tilesP = (int)((M + 2 * kBM - 1) / (2 * kBM));
     p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
-    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
-    if ((rc = make_packed_map(&tmQ, B, N, K / 2, kBN2 / 2))) return rc;
     // tiled stores need a 16-byte aligned base and row pitch; otherwise the epilogue stores element-wise
     OutMaps tmO;
+    CUtensorMap tmTail;
     p.tma_out = aligned16(out) && (ldo % (MODE == MODE_I32 ? 4 : 8) == 0) && g_tuning.gemm_tma_out != 0;
     p.n_outs = 1;
+    // Tile width.  The persistent clusters take the pair tiles in waves, and a last wave that is half empty costs as
+    // much as a full one; a slightly narrower tile often fills the waves (4096 x 12288 on 74 clusters: 384 tiles of
+    // 256 columns = 6 waves of 256, 440 tiles of 224 columns = 6 waves of 224).  The width that minimises
+    // waves x (width + a fixed per-tile cost) is taken; widths other than 256 need the fp16 epilogue with tiled stores.
+    p.bn = kBN2;
+    if (MODE == MODE_F16 && !swiglu && n_more == 0 && p.tma_out && g_tuning.gemm_bn2 != 256) {
+      int clusters = num_sms() / 2;
+      if (grid_cap > 0 && clusters > grid_cap) clusters = grid_cap;
+      long long best = -1;
+      for (int bn : kPairWidths) {
+        if (g_tuning.gemm_bn2 != 0 && g_tuning.gemm_bn2 != bn) continue;     // a width forced through the knob
+        const long long tiles = (long long)p.tilesP * ((N + bn - 1) / bn);
+        const long long cost = ((tiles + clusters - 1) / clusters) * (bn + 8);
+        if (best < 0 || cost < best) { best = cost; p.bn = bn; }
+      }
+    }
+    p.tilesQ = (int)((N + p.bn - 1) / p.bn);
+    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
+    if ((rc = make_packed_map(&tmQ, B, N, K / 2, p.bn / 2))) return rc;
     if (swiglu) {
       p.swiglu = 1; p.tma_out = 1;
       if ((rc = make_out_map(&tmO.m[0], out, M, N / 2, ldo, false))) return rc;
     } else if (p.tma_out) {
       if ((rc = make_out_map(&tmO.m[0], out, M, N, ldo, MODE == MODE_I32))) return rc;
+      if (p.bn % 64 != 0 && (rc = make_out_map(&tmTail, out, M, N, ldo, false, true))) return rc;
       for (int g = 0; g < n_more; ++g) {
         if (!aligned16(more_outs[g])) return fail(QR_EALIGN, "%s: every output must be 16-byte aligned", who);
         if ((rc = make_out_map(&tmO.m[1 + g], more_outs[g], M, N, ldo, MODE == MODE_I32))) return rc;
@@ -1090,56 +1065,36 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
       tmO.m[0] = tmP;   // never dereferenced
     }
     for (int g = p.n_outs; g < kMaxOuts; ++g) tmO.m[g] = tmO.m[0];
-    return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, tmO, p, grid_cap, st);
+    if (p.bn % 64 == 0) tmTail = tmO.m[0];   // never dereferenced
+    return launch_gemm_2sm<4, 4, MODE>(tmP, tmQ, tmO, tmTail, p, grid_cap, st);
   }
-  if (!swap) {
-    int bn = g_tuning.gemm_bn;
-    if (bn != 256 && bn != 128 && bn != 64) bn = 256;
-    p.rowsP = (int)M; p.rowsQ = (int)N;
-    p.tilesP = (int)((M + kBM - 1) / kBM); p.tilesQ = (int)((N + bn - 1) / bn);
-    p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
-    if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
-    if ((rc = make_packed_map(&tmQ, B, N, K / 2, bn))) return rc;
-    const int pst = g_tuning.gemm_pst;
-    if (bn == 256) {
-      if (pst == 3) return launch_gemm<256, 3, 3, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
-      return launch_gemm<256, 4, 2, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
+  if (M <= g_tuning.gemm_decode_max_m && !swiglu && n_more == 0) {
+    // a handful of token rows: one pass over the weights on the CUDA cores, no tensor-core fixed costs
+    if (M <= g_tuning.gemv_max_m) {
+      rc = launch_gemv_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
+      if (rc != QR_EUNSUPPORTED) return rc;
     }
-    if (bn == 128) return launch_gemm<128, 4, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
-    return launch_gemm<64, 6, 4, 2, false, MODE>(tmP, tmQ, p, grid_cap, st);
-  }
-  // a handful of token rows: one pass over the weights on the CUDA cores, no tensor-core fixed costs
-  if (M <= g_tuning.gemv_max_m) {
-    rc = launch_gemv_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
-    if (rc != QR_EUNSUPPORTED) return rc;
-  }
-  // decode-sized M: weights fill the MMA rows, tokens are the MMA columns; with a scratch buffer the K
-  // loop of a tile is split over several CTAs so that all SMs stream weights
-  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
-  if (ws && g_tuning.gemm_splitk != 0) {
-    size_t need = 0, compact_counters = 0;
-    int splits = decode_splits(M, N, K, &need, &compact_counters, !compact_ws);
-    if (!compact_ws) {   // fixed counter region in front of the partial tiles
-      if (compact_counters > kWsCounterRegion) splits = 1;
-      need = need - compact_counters + kWsCounterRegion;
-    }
-    if (splits > 1) {
-      if (ws_bytes < need) return fail(QR_EINVAL, "%s: workspace of %zu bytes is too small, %zu needed", who, ws_bytes, need);
-      if (((uintptr_t)ws & 255) != 0) return fail(QR_EALIGN, "%s: workspace must be 256-byte aligned", who);
-      p.splits = splits;
-      p.ws_counter = reinterpret_cast<int*>(ws);
-      p.ws_partial = reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(ws) +
-                                                (compact_ws ? compact_counters : kWsCounterRegion));
+    // decode-sized M on the tensor cores: weights on the MMA rows, all SMs streaming (gemm_i4_decode.cu)
+    if (g_tuning.gemm_decode != 0) {
+      rc = launch_gemm_i4_decode(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, grid_cap, ws, ws_bytes, st);
+      if (rc != QR_EUNSUPPORTED) return rc;
     }
   }
-  p.rowsP = (int)N; p.rowsQ = (int)M;
-  p.tilesP = (int)((N + kBM - 1) / kBM); p.tilesQ = (int)((M + bn - 1) / bn);
-  p.sP = reinterpret_cast<const __half*>(sB); p.sQ = reinterpret_cast<const __half*>(sA);
-  if ((rc = make_packed_map(&tmP, B, N, K / 2, kBM))) return rc;
-  if ((rc = make_packed_map(&tmQ, A, M, K / 2, bn))) return rc;
-  if (bn == 16) return launch_gemm<16, 8, 4, 2, true, MODE>(tmP, tmQ, p, grid_cap, st);
-  if (bn == 32) return launch_gemm<32, 8, 4, 2, true, MODE>(tmP, tmQ, p, grid_cap, st);
-  return launch_gemm<64, 6, 4, 2, true, MODE>(tmP, tmQ, p, grid_cap, st);
+  // everything else (up to 128 token rows, or the 2-CTA kernel switched off): tokens on the 128 MMA rows of one CTA
+  int bn = g_tuning.gemm_bn;
+  if (bn != 256 && bn != 128 && bn != 64) bn = 256;
+  p.rowsP = (int)M; p.rowsQ = (int)N;
+  p.tilesP = (int)((M + kBM - 1) / kBM); p.tilesQ = (int)((N + bn - 1) / bn);
+  p.sP = reinterpret_cast<const __half*>(sA); p.sQ = reinterpret_cast<const __half*>(sB);
+  if ((rc = make_packed_map(&tmP, A, M, K / 2, kBM))) return rc;
+  if ((rc = make_packed_map(&tmQ, B, N, K / 2, bn))) return rc;
+  const int pst = g_tuning.gemm_pst;
+  if (bn == 256) {
+    if (pst == 3) return launch_gemm<256, 3, 3, 2, MODE>(tmP, tmQ, p, grid_cap, st);
+    return launch_gemm<256, 4, 2, 2, MODE>(tmP, tmQ, p, grid_cap, st);
+  }
+  if (bn == 128) return launch_gemm<128, 4, 4, 2, MODE>(tmP, tmQ, p, grid_cap, st);
+  return launch_gemm<64, 6, 4, 2, MODE>(tmP, tmQ, p, grid_cap, st);
 }
 
 }  // namespace qr
@@ -1164,35 +1119,27 @@ int qr_linear_i4_f16_outs(const uint8_t* A, const void* sA, const uint8_t* B, co
   for (int g = 0; g < n_outs; ++g)
     if (!outs[g]) return qr::fail(QR_EINVAL, "qr_linear_i4_f16_outs: null output %d", g);
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_outs", A, B, M, N, K, outs[0], ldo, sA, sB, bias,
-                                    (cudaStream_t)stream, nullptr, 0, false, outs + 1, n_outs - 1);
+                                    (cudaStream_t)stream, nullptr, 0, outs + 1, n_outs - 1);
 }
 
 int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB,
                             int64_t M, int64_t N2, int64_t K, void* out, int64_t ldo, void* stream) {
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_swiglu_f16", A, B, M, N2, K, out, ldo, sA, sB, nullptr,
-                                    (cudaStream_t)stream, nullptr, 0, false, nullptr, 0, true);
+                                    (cudaStream_t)stream, nullptr, 0, nullptr, 0, true);
 }
 
-// scratch of the decode path (split-K) in the compact layout of the built-in array of qr_linear_i4_f16_static
-static size_t decode_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  if (M <= 0 || N <= 0 || K <= 0 || M > qr::g_tuning.gemm_swap_max_m) return 0;
-  size_t bytes = 0;
-  qr::decode_splits(M, N, K, &bytes);
-  return bytes;
-}
-
+// Scratch bytes a decode-sized call wants: narrow layers only (their (tile, stage) units are dealt out to the
+// SMs and pieces of a tile meet in scratch memory); everything else runs without scratch.
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-  if (M <= 0 || N <= 0 || K <= 0 || M > qr::g_tuning.gemm_swap_max_m) return 0;
-  size_t bytes = 0, compact_counters = 0;
-  if (qr::decode_splits(M, N, K, &bytes, &compact_counters, true) <= 1 || compact_counters > qr::kWsCounterRegion) return 0;
-  return bytes - compact_counters + qr::kWsCounterRegion;
+  if (M <= qr::g_tuning.gemv_max_m || M > qr::g_tuning.gemm_decode_max_m || qr::g_tuning.gemm_decode == 0) return 0;
+  return qr::decode_stream_workspace_bytes(M, N, K);
 }
 
 // ---- scratch that lives inside the library image (see qr_linear_i4_f16_static) -----------------
 // In host code the array's name is only a handle: the device address has to be asked for with
 // cudaGetSymbolAddress, once per device and with that device current.
 namespace qr {
-constexpr size_t kStaticScratchBytes = (4u << 20) + 4096;   // partial tiles of the LLaMA decode shapes + counters
+constexpr size_t kStaticScratchBytes = (1u << 20) + (64u << 10);   // 64 KiB of arrival counters + 1 MiB of int32 sums
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 static int static_scratch_ptr(void** out) {
@@ -1214,24 +1161,26 @@ static int static_scratch_ptr(void** out) {
 
 int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,
                             int64_t M, int64_t N, int64_t K, void* out, int64_t ldo, void* stream) {
-  const size_t need = decode_workspace_bytes(M, N, K);
+  const size_t need = qr_linear_workspace_bytes(M, N, K);
   if (need > qr::kStaticScratchBytes)
     return qr::fail(QR_EUNSUPPORTED,
                     "qr_linear_i4_f16_static: this shape needs %zu bytes of scratch, the built-in scratch holds %zu; "
                     "use qr_linear_i4_f16_ws with a caller-provided workspace", need, qr::kStaticScratchBytes);
-  if (need == 0)   // shape runs in a single pass, no scratch involved
+  if (need == 0)   // shape runs without scratch
     return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_static", A, B, M, N, K, out, ldo, sA, sB, bias,
                                       (cudaStream_t)stream);
   void* scratch = nullptr;
   const int rc = qr::static_scratch_ptr(&scratch);
   if (rc != QR_OK) return rc;
-  // every call shares the array and finds the previous call's contents in it: the arrival counters at its
-  // start must be zero when the kernel begins (the partial tiles behind them are fully overwritten)
-  size_t counter_bytes = 0;
-  qr::decode_splits(M, N, K, nullptr, &counter_bytes);
-  QR_CUDA(cudaMemsetAsync(scratch, 0, counter_bytes, (cudaStream_t)stream));
+  // Every call shares the array and finds the previous call's contents in it.  A call that ran to its end leaves
+  // the part it used at zero, but nothing says that the previous call did (a different shape, a kernel that gave
+  // up on a wait): the counters and sums this shape uses are cleared on the caller's stream first.
+  const size_t tiles = (size_t)((N + 127) / 128);
+  const size_t counters = 64u << 10;
+  QR_CUDA(cudaMemsetAsync(scratch, 0, tiles * sizeof(int), (cudaStream_t)stream));
+  QR_CUDA(cudaMemsetAsync(static_cast<unsigned char*>(scratch) + counters, 0, need - counters, (cudaStream_t)stream));
   return qr::run_gemm<qr::MODE_F16>("qr_linear_i4_f16_static", A, B, M, N, K, out, ldo, sA, sB, bias,
-                                    (cudaStream_t)stream, scratch, qr::kStaticScratchBytes, true);
+                                    (cudaStream_t)stream, scratch, qr::kStaticScratchBytes);
 }
 
 int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, const void* sB, const void* bias,

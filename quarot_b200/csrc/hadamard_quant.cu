@@ -36,6 +36,10 @@ namespace qr {
 int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k, float clip, uint8_t* q,
                    void* scales, void* y_out, int do_quant, cudaStream_t st);
 
+// warp-per-row Walsh kernel for n = 256 .. 4096 (hadamard_walsh.cu); QR_EUNSUPPORTED means "not my shape"
+int launch_hadq_walsh(const void* x, int64_t rows, int n, int64_t ldx, uint32_t stage_mask, float scale, float clip,
+                      uint8_t* q, void* scales, void* y_out, int64_t ldy, int do_quant, cudaStream_t st);
+
 struct HadqParams {
   const void* x;
   int64_t ldx;        // elements between work items
@@ -602,7 +606,7 @@ static int launch_fast(const HadqParams& p, int threads, size_t smem, cudaStream
     if (dev < 64) configured[dev] = smem;
   }
   QR_CUDA(launch_kernel(hadq_fast_kernel<KT>, dim3(persistent_grid(p.rows, threads, smem)), dim3(threads), smem, st,
-                        g_tuning.pdl != 0, p));
+                        use_pdl(p.rows), p));
   return QR_OK;
 }
 
@@ -622,7 +626,7 @@ static int launch_generic(const HadqParams& p, cudaStream_t st) {
   if (per_sm < 1) per_sm = 1;
   int64_t grid = (int64_t)num_sms() * per_sm;
   if (grid > p.rows) grid = p.rows;
-  QR_CUDA(launch_kernel(hadq_generic_kernel<T>, dim3((int)grid), dim3(256), smem, st, g_tuning.pdl != 0, p));
+  QR_CUDA(launch_kernel(hadq_generic_kernel<T>, dim3((int)grid), dim3(256), smem, st, use_pdl(p.rows), p));
   return QR_OK;
 }
 
@@ -665,11 +669,15 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
   if (base_ok && K == 0 && do_quant && n >= 64) {
     int threads = ((n / 8 + 3) / 4 + 31) / 32 * 32;
     QR_CUDA(launch_kernel(quant_rows_kernel, dim3(persistent_grid(rows, threads, 1024)), dim3(threads), 0, st,
-                          g_tuning.pdl != 0, p));
+                          use_pdl(p.rows), p));
     return QR_OK;
   }
   if (base_ok && K > 1 && m == 64 && ldx == n && g_tuning.hadq_tc != 0) {
     const int rc = launch_hadq_tc(x, rows, n, K, had_k, clip, q, scales, y_out, do_quant, st);
+    if (rc != QR_EUNSUPPORTED) return rc;
+  }
+  if (base_ok && K == 1 && n >= 256 && n <= 4096 && g_tuning.hadq_walsh != 0) {
+    const int rc = launch_hadq_walsh(x, rows, n, ldx, (uint32_t)(n - 1), p.scale, clip, q, scales, y_out, n, do_quant, st);
     if (rc != QR_EUNSUPPORTED) return rc;
   }
   bool fast = base_ok && K >= 1 && (n % 32 == 0) && (!do_quant || (n % 32 == 0));

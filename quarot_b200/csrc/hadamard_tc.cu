@@ -416,7 +416,7 @@ int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k,
   }
   int64_t grid = num_sms();
   if (grid > (rows + 1) / 2) grid = (rows + 1) / 2;
-  QR_CUDA(launch_kernel(hadq_tc_kernel, dim3((int)grid), dim3(kTcThreads), (size_t)smem, st, g_tuning.pdl != 0, tm, p));
+  QR_CUDA(launch_kernel(hadq_tc_kernel, dim3((int)grid), dim3(kTcThreads), (size_t)smem, st, use_pdl(rows), tm, p));
   return QR_OK;
 }
 

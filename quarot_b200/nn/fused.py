@@ -96,8 +96,10 @@ class RMSNormQuantizer(torch.nn.Module):
 
 class QuantLinear4bit(torch.nn.Module):
     """Sequential(Quantizer, Linear4bit) as one module: with one or two token rows (single-sequence decode) the
-    quantiser runs inside the weight-streaming kernel, otherwise the two modules run one after the other (every
-    CTA of the fused kernel quantises all rows itself, which stops paying off at four rows: measured)."""
+    quantiser runs inside the weight-streaming CUDA-core kernel, otherwise the two modules run one after the other
+    (every CTA of the fused kernel quantises all rows itself, which stops paying off at four rows: measured)."""
+
+    FUSED_MAX_ROWS = 2     # measured cross-over between one launch and two
 
     def __init__(self, quantizer, linear):
         super().__init__()
@@ -105,7 +107,7 @@ class QuantLinear4bit(torch.nn.Module):
 
     def forward(self, x):
         rows = x.numel() // x.shape[-1]
-        if rows <= 2 and x.dtype == torch.float16:
+        if rows <= self.FUSED_MAX_ROWS and x.dtype == torch.float16:
             return _ops.quant_linear_i4(x, self.linear.weight, self.linear.weight_scales, self.linear.bias,
                                         self.quantizer.input_clip_ratio)
         return self.linear(self.quantizer(x))

@@ -65,6 +65,10 @@ def test_matmul_leading_dims_and_errors():
 
 TILE_CONFIGS = {
     "2sm_ss_grid3": {"gemm_grid": 3},
+    "2sm_bn256": {"gemm_bn2": 256},
+    "2sm_bn240": {"gemm_bn2": 240},
+    "2sm_bn224_grid3": {"gemm_bn2": 224, "gemm_grid": 3},
+    "2sm_bn192": {"gemm_bn2": 192},
     "2sm_ss_elementwise_stores": {"gemm_tma_out": 0},
     "1sm_bn256": {"gemm_2sm": 0},
     "1sm_bn128": {"gemm_2sm": 0, "gemm_bn": 128},
@@ -72,7 +76,7 @@ TILE_CONFIGS = {
     "1sm_pst3": {"gemm_2sm": 0, "gemm_pst": 3},
     "1sm_grid3": {"gemm_2sm": 0, "gemm_grid": 3},
 }
-TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0, "gemm_tma_out": 1}
+TILE_DEFAULTS = {"gemm_2sm": 1, "gemm_bn2": 0, "gemm_bn": 256, "gemm_pst": 4, "gemm_grid": 0, "gemm_tma_out": 1}
 
 
 @pytest.mark.parametrize("tiles", sorted(TILE_CONFIGS))
@@ -81,16 +85,19 @@ def test_matmul_other_tile_configs_agree(tiles):
     want = O.matmul_i4(a, b)
     sx = (torch.rand(300) * 0.5 + 0.05).half()
     sw = (torch.rand(1000) * 0.015 + 0.005).half()
+    bias = (torch.randn(1000) * 0.5).half()
     for k, v in TILE_CONFIGS[tiles].items():
         _lib.set_tuning(k, v)
     try:
         c = qb.matmul(a.to(DEV), b.to(DEV)).cpu()
         o = qb.linear_i4(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV)).cpu()
+        ob = qb.linear_i4(a.to(DEV), sx.to(DEV), b.to(DEV), sw.to(DEV), bias.to(DEV)).cpu()
     finally:
         for k, v in TILE_DEFAULTS.items():
             _lib.set_tuning(k, v)
     assert torch.equal(c, want)
     assert torch.equal(o, O.sym_dequant_fp32(want, sx, sw).half())
+    assert torch.equal(ob, O.sym_dequant_fp32(want, sx, sw).half() + bias)
     assert _lib.kernel_status() == 0
 
 
@@ -211,38 +218,49 @@ def test_full_size_config0_properties():
     assert _lib.kernel_status() == 0
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (8, 4096, 4096), (32, 4096, 11008), (24, 4096, 4096),
-                                   (17, 1000, 2048), (32, 512, 28672)])
-def test_decode_split_k_matches_single_pass(M, N, K):
-    """Decode-sized M: the K loop is split over CTAs through the scratch buffer; same bits as one pass."""
+@pytest.mark.parametrize("M,N,K", [(5, 4096, 4096), (8, 4096, 4096), (32, 4096, 11008), (24, 4096, 4096),
+                                   (17, 1000, 2048), (32, 512, 28672), (64, 7000, 1024)])
+def test_decode_unit_split_matches_row_split(M, N, K):
+    """Decode-sized M on a narrow layer: with scratch memory the (tile, stage) units are dealt out to the SMs and pieces
+    of a tile are summed with integer atomics; without it the weight rows are dealt out.  Same bits, also over repeated
+    launches (the kernel leaves counters and sums at zero) and against the kernel that puts the tokens on the MMA rows."""
     g = torch.Generator().manual_seed(M + K)
     a, w = _rand_packed(M, K, 11), _rand_packed(N, K, 12)
     sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
     sw = (torch.rand(N, generator=g) * 0.015 + 0.005).half()
     bias = (torch.randn(N, generator=g) * 0.5).half()
-    need = _lib.lib.qr_linear_workspace_bytes(M, N, K)
-    assert need > 0
+    assert _lib.lib.qr_linear_workspace_bytes(M, N, K) > 0
     ad, wd, sxd, swd, bd = a.to(DEV), w.to(DEV), sx.to(DEV), sw.to(DEV), bias.to(DEV)
     ref = O.sym_dequant_fp32(O.matmul_i4(a, w), sx, sw).half() + bias
-    # M <= 8 is normally served by the weight-streaming kernel; gemv_max_m = 0 sends it through the tensor cores
-    for gemv_max_m in (8, 0):
-        _lib.set_tuning("gemv_max_m", gemv_max_m)
-        try:
-            one = qb.linear_i4(ad, sxd, wd, swd, bd, use_workspace=False)
-            for _ in range(3):   # repeated launches: the arrival counters must come back to zero
-                split = qb.linear_i4(ad, sxd, wd, swd, bd)
-                assert torch.equal(split, one)
-        finally:
-            _lib.set_tuning("gemv_max_m", 8)
-        assert torch.equal(one.cpu(), ref)
+    one = qb.linear_i4(ad, sxd, wd, swd, bd, use_workspace=False)
+    for _ in range(3):
+        assert torch.equal(qb.linear_i4(ad, sxd, wd, swd, bd), one)
+    assert torch.equal(one.cpu(), ref)
+    _lib.set_tuning("gemm_decode", 0)
+    _lib.set_tuning("gemv_max_m", 0)
+    try:
+        assert _lib.lib.qr_linear_workspace_bytes(M, N, K) == 0
+        assert torch.equal(qb.linear_i4(ad, sxd, wd, swd, bd), one)
+    finally:
+        _lib.set_tuning("gemm_decode", 1)
+        _lib.set_tuning("gemv_max_m", 4)
     assert _lib.kernel_status() == 0
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (2, 1000, 2048), (3, 12288, 4096), (5, 4096, 11008), (8, 22016, 4096),
                                    (7, 33, 64), (8, 8192, 28672), (1, 1, 64)])
 def test_weight_streaming_kernel_for_a_few_rows(M, N, K):
-    """M <= 8: one pass over the packed weights with dp4a on the CUDA cores; exact accumulators and the same
-    dequantisation arithmetic as the tensor-core kernels."""
+    """M <= 8 on the CUDA-core kernel (it serves up to four rows by default; gemv_max_m = 8 sends all of these shapes
+    to it): one pass over the packed weights with dp4a; exact accumulators and the same dequantisation arithmetic as
+    the tensor-core kernels."""
+    _lib.set_tuning("gemv_max_m", 8)
+    try:
+        _weight_streaming_case(M, N, K)
+    finally:
+        _lib.set_tuning("gemv_max_m", 4)
+
+
+def _weight_streaming_case(M, N, K):
     g = torch.Generator().manual_seed(M * 7 + N)
     a, w = _rand_packed(M, K, 61), _rand_packed(N, K, 62)
     sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
@@ -267,7 +285,9 @@ def test_workspace_argument_errors():
     rc = _lib.lib.qr_linear_i4_f16_ws(a.data_ptr(), sx.data_ptr(), w.data_ptr(), sw.data_ptr(), None, 16, 4096, 4096,
                                       out.data_ptr(), 4096, small.data_ptr(), small.numel(), None)
     assert rc == -1 and "workspace" in _lib.last_error() and need > 256
-    assert _lib.lib.qr_linear_workspace_bytes(2048, 4096, 4096) == 0     # prefill shapes never split
+    assert _lib.lib.qr_linear_workspace_bytes(2048, 4096, 4096) == 0     # prefill shapes need no scratch
+    assert _lib.lib.qr_linear_workspace_bytes(16, 12288, 4096) == 0      # nor do wide layers at decode sizes
+    assert _lib.lib.qr_linear_workspace_bytes(2, 4096, 4096) == 0        # nor the CUDA-core kernel
 
 
 def test_one_workspace_serves_calls_of_different_shapes():
@@ -376,3 +396,37 @@ def test_quantizer_inside_the_weight_streaming_kernel(M, N, K, clip):
     assert torch.equal(QuantLinear4bit(quant, lin)(xb), lin(quant(xb)))
     assert _lib.kernel_status() == 0
 
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (3, 12288, 4096), (5, 4096, 11008), (8, 22016, 4096), (16, 4096, 4096),
+                                   (13, 1000, 2048), (16, 8192, 28672), (9, 33, 1024), (16, 7, 4096), (12, 300, 1088), (32, 4096, 4096), (64, 22016, 4096), (40, 4096, 11008), (33, 1000, 256), (64, 130, 320),
+                                   (16, 20000, 1024)])
+def test_weight_streaming_tensor_core_kernel(M, N, K):
+    """Decode-sized M on the tensor cores: (tile, stage) units dealt out evenly to the SMs, pieces of a tile summed in
+    scratch memory with integer atomics.  gemv_max_m = 0 routes the shapes the CUDA-core kernel would otherwise take
+    through it as well.  Exact accumulators, the epilogue arithmetic of the other kernels; the same bits with and
+    without scratch memory, with programmatic dependent launch switched on, and over repeated launches (the kernel
+    leaves its scratch at zero)."""
+    g = torch.Generator().manual_seed(M * 31 + N)
+    a, w = _rand_packed(M, K, 71), _rand_packed(N, K, 72)
+    sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand(N, generator=g) * 0.015 + 0.005).half()
+    bias = (torch.randn(N, generator=g) * 0.5).half()
+    acc = O.matmul_i4(a, w)
+    ad, wd = a.to(DEV), w.to(DEV)
+    _lib.set_tuning("gemv_max_m", 0)
+    try:
+        for pdl in (0, 1):
+            _lib.set_tuning("pdl", pdl)
+            assert torch.equal(qb.matmul(ad, wd).cpu(), acc)
+            out = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), bias.to(DEV))
+            assert torch.equal(out.cpu(), O.sym_dequant_fp32(acc, sx, sw).half() + bias)
+            for _ in range(2):
+                out2 = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV))
+                assert torch.equal(out2.cpu(), O.sym_dequant_fp32(acc, sx, sw).half())
+            out3 = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), use_workspace=False)
+            assert torch.equal(out3.cpu(), O.sym_dequant_fp32(acc, sx, sw).half())
+    finally:
+        _lib.set_tuning("gemv_max_m", 4)
+        _lib.set_tuning("pdl", 2)
+    assert _lib.kernel_status() == 0

@@ -172,3 +172,22 @@ def test_new_entry_points_validate_arguments_without_gpu():
     assert lib.qr_linear_i4_f16_outs(None, None, None, None, None, 256, 256, 256, None, 1, 256, None) == -1
     assert "outputs" in _lib.last_error()
 
+
+
+def test_bench_tables_and_cpu_generators_match_synth():
+    """bench.py repeats the layer tables and the CPU generators of quarot_b200/synth.py so that its reference arm
+    runs without importing the product package; they must stay identical."""
+    import importlib.util
+    from quarot_b200 import synth
+    spec = importlib.util.spec_from_file_location("_bench_for_test", os.path.join(ROOT, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    for name, table in bench.LAYERS.items():
+        assert table == getattr(synth, name), name
+    assert torch.equal(bench._cpu_activations(O, 5, 256, 1234), synth.activations(5, 256, seed=1234))
+    w, s = bench._cpu_weights(O, 7, 64, 4321)
+    w2, s2 = synth.weights(7, 64, seed=4321)
+    assert torch.equal(w, w2) and torch.equal(s, s2)
+    src = open(os.path.join(ROOT, "bench.py")).read()
+    ref_arm = src[src.index("def cpu_reference_run"):src.index("# ------------------------------------------------------------------ device arm")]
+    assert "quarot_b200" not in ref_arm.replace("quarot_b200/synth.py", "")

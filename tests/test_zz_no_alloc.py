@@ -21,7 +21,7 @@ from quarot_b200.functional.quantization import pack_i4
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
-LIMIT = (4 << 20) + 4096      # size of the scratch array inside the library
+LIMIT = (1 << 20) + (64 << 10)      # size of the scratch array inside the library
 
 
 def _inputs(M, N, K, seed):
@@ -44,9 +44,10 @@ def _call(fn, a, sa, w, sw, bias, M, N, K):
     return out
 
 
-@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (64, 4096, 11008)])
+@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (32, 4096, 4096), (64, 4096, 11008)])
 def test_static_scratch_entry_matches_ordinary_entry_twice(M, N, K):
     lib = _lib.lib
+    assert 0 < lib.qr_linear_workspace_bytes(M, N, K) <= LIMIT           # these shapes do use the array
     first = _inputs(M, N, K, seed=1)
     second = _inputs(M, N, K, seed=2)
     for args in (first, second):                                        # two calls in a row share the array
@@ -56,17 +57,40 @@ def test_static_scratch_entry_matches_ordinary_entry_twice(M, N, K):
     assert _lib.kernel_status() == 0
 
 
+def test_static_scratch_entry_calls_of_different_shapes_share_the_array_and_allocate_nothing():
+    lib = _lib.lib
+    shapes = [(64, 4096, 4096), (16, 1000, 2048), (32, 4096, 11008), (16, 1000, 2048), (64, 4096, 4096)]
+    cases = [(_inputs(M, N, K, seed=5 + i), (M, N, K)) for i, (M, N, K) in enumerate(shapes)]
+    wants = [_call(lib.qr_linear_i4_f16, *args, *shape) for (args, shape) in cases]
+    _call(lib.qr_linear_i4_f16_static, *cases[0][0], *cases[0][1])       # first call on the device: address look-up
+    outs = [torch.full((M, N), float("nan"), dtype=torch.float16, device=DEV) for (M, N, K) in shapes]
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    stream = torch.cuda.current_stream().cuda_stream
+    for (args, (M, N, K)), out in zip(cases, outs):                      # back to back on one stream, no host sync between
+        a, sa, w, sw, bias = args
+        rc = lib.qr_linear_i4_f16_static(a.data_ptr(), sa.data_ptr(), w.data_ptr(), sw.data_ptr(), bias.data_ptr(), M, N, K,
+                                         out.data_ptr(), N, stream)
+        assert rc == 0, _lib.last_error()
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before                   # the calls took no device memory
+    for out, want in zip(outs, wants):
+        assert torch.equal(out, want)
+    assert _lib.kernel_status() == 0
+
+
 def test_static_scratch_entry_refuses_what_does_not_fit():
     lib = _lib.lib
-    # 37 tiles of 128 output channels x 4 k splits x (128 x 64 int32) = 4.6 MiB of partial tiles: too much
-    M, N, K = 64, 37 * 128, 4096
+    # 40 tiles of 128 output channels x (128 x 64 int32 sums) = 1.25 MiB: more than the array holds
+    M, N, K = 64, 5120, 5120
+    assert lib.qr_linear_workspace_bytes(M, N, K) > LIMIT
     dummy = torch.zeros(16, dtype=torch.uint8, device=DEV)
     p = dummy.data_ptr()
     rc = lib.qr_linear_i4_f16_static(p, p, p, p, None, M, N, K, p, N, None)
     assert rc == -3 and "built-in scratch" in _lib.last_error()
-    # a shape that needs no scratch at all is simply run in one pass
-    a, sa, w, sw, bias = _inputs(8, 24576, 256, seed=3)
-    assert lib.qr_linear_workspace_bytes(8, 24576, 256) == 0
-    want = _call(lib.qr_linear_i4_f16, a, sa, w, sw, bias, 8, 24576, 256)
-    got = _call(lib.qr_linear_i4_f16_static, a, sa, w, sw, bias, 8, 24576, 256)
+    # a shape that needs no scratch at all (a wide layer: the weight rows are dealt out to the SMs) is simply run
+    a, sa, w, sw, bias = _inputs(16, 24576, 1024, seed=3)
+    assert lib.qr_linear_workspace_bytes(16, 24576, 1024) == 0
+    want = _call(lib.qr_linear_i4_f16, a, sa, w, sw, bias, 16, 24576, 1024)
+    got = _call(lib.qr_linear_i4_f16_static, a, sa, w, sw, bias, 16, 24576, 1024)
     assert torch.equal(got, want)
