@@ -80,6 +80,16 @@ int qr_hadamard_f16(const void* x, void* y, int64_t rows, int64_t n,
 int qr_hadamard_f32(const float* x, float* y, int64_t rows, int64_t n,
                     const void* had_k, int K, void* stream);
 
+/* Walsh-Hadamard transform over the LEADING axis of rows that are [heads, head_dim] matrices:
+ *   y[h', d] = sum_h (-1)^popcount(h & h') x[h, d] / sqrt(heads)        for every row and every d.
+ * This is OnlineHadamard(num_heads) applied to the transposed view attn_output.transpose(-1, -2) and transposed
+ * back, as the attention block does in front of o_proj (e2e/quantized_llama/modeling_llama.py:82 with
+ * quarot/nn/hadamard.py:17-23), without materialising the transposed tensor: one read and one write of the data.
+ *   x, y : [rows, heads, head_dim] fp16, contiguous, 16-byte aligned; y may alias x
+ *   heads and head_dim powers of two, head_dim >= 32, 256 <= heads * head_dim <= 4096 (QR_EUNSUPPORTED otherwise:
+ *   transform a contiguous copy of the transposed view with qr_hadamard_f16). */
+int qr_hadamard_heads_f16(const void* x, void* y, int64_t rows, int64_t heads, int64_t head_dim, void* stream);
+
 /* Fused [online Hadamard ->] per-token absmax scale -> INT4 quantise -> pack.
  * Replaces OnlineHadamard.forward + Quantizer.forward
  * (quarot/nn/hadamard.py:17-23, quarot/nn/quantization.py:9-13) including the

@@ -27,6 +27,7 @@ SIGNATURES = {
     "qr_debug_division_check": (_int, [ctypes.POINTER(ctypes.c_uint64)]),
     "qr_hadamard_f16": (_int, [_vp, _vp, _i64, _i64, _vp, _int, _vp]),
     "qr_hadamard_f32": (_int, [_vp, _vp, _i64, _i64, _vp, _int, _vp]),
+    "qr_hadamard_heads_f16": (_int, [_vp, _vp, _i64, _i64, _i64, _vp]),
     "qr_hadamard_quant_i4": (_int, [_vp, _i64, _i64, _i64, _vp, _int, _f32, _vp, _vp, _vp, _vp]),
     "qr_sym_quant_i4": (_int, [_vp, _vp, _i64, _i64, _vp, _vp]),
     "qr_matmul_i4_i32": (_int, [_vp, _vp, _i64, _i64, _i64, _vp, _vp]),

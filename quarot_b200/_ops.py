@@ -111,8 +111,31 @@ class PackedQuantizedTensor:
 
 
 # ------------------------------------------------------------------ fused entry points
+def _heads_axis_view(x, K):
+    """(base, heads, head_dim) when x is the transposed view [..., head_dim, heads] of a contiguous fp16 tensor
+    [..., heads, head_dim] that the heads-axis kernel serves (what the attention block hands to its Hadamard in front
+    of o_proj), else None."""
+    if K != 1 or x.dim() < 2 or x.dtype != torch.float16 or x.is_contiguous():
+        return None
+    base = x.transpose(-1, -2)
+    heads, hd = base.shape[-2], base.shape[-1]
+    n = heads * hd
+    if not base.is_contiguous() or heads & (heads - 1) or hd & (hd - 1) or hd < 32 or not 256 <= n <= 4096:
+        return None
+    return base, heads, hd
+
+
 def hadamard(x, had_k=None, K=1):
     """Online Hadamard over the last axis of an fp16/fp32 CUDA tensor (one kernel)."""
+    tv = _heads_axis_view(x, K) if x.is_cuda else None
+    if tv is not None:
+        base, heads, hd = tv
+        with torch.cuda.device(base.device):
+            y = torch.empty_like(base)
+            rows = base.numel() // (heads * hd)
+            _lib.check(_lib_c.qr_hadamard_heads_f16(base.data_ptr(), y.data_ptr(), rows, heads, hd, _stream(base.device)),
+                       "hadamard (heads axis)")
+        return y.transpose(-1, -2)
     x2, shape_excl_last = flatten_last_dim_and_return_shape(x.contiguous())
     dev = _check_cuda_contig("hadamard", x=x2, had_k=had_k)
     rows, n = x2.shape

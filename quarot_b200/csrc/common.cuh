@@ -31,7 +31,7 @@ struct Tuning {
   int gemm_decode = 1;        // decode: the weight-streaming tcgen05 kernel (0: tokens on the MMA rows as at prefill)
   int pdl = 2;                // programmatic dependent launch: 0 never, 1 always, 2 decode-sized launches only
   int hadq_path = 0;          // 1 = always the generic Hadamard kernel (A/B checks)
-  int hadq_walsh = 1;         // warp-per-row register kernel for Walsh lengths 256 .. 4096
+  int hadq_walsh = 0;         // 1: warp-per-row register kernel also for whole-row Walsh transforms of 256 .. 4096 (measured slower)
   int hadq_tc = 1;            // tensor-core kernel for n = 64 K Kronecker shapes
 };
 extern Tuning g_tuning;

@@ -736,6 +736,21 @@ int qr_hadamard_f32(const float* x, float* y, int64_t rows, int64_t n, const voi
                       (cudaStream_t)stream);
 }
 
+int qr_hadamard_heads_f16(const void* x, void* y, int64_t rows, int64_t heads, int64_t head_dim, void* stream) {
+  if (rows < 0 || heads < 1 || head_dim < 1) return qr::fail(QR_EINVAL, "qr_hadamard_heads_f16: bad size");
+  if (rows == 0) return QR_OK;
+  if (!x || !y) return qr::fail(QR_EINVAL, "qr_hadamard_heads_f16: null pointer");
+  const int64_t n = heads * head_dim;
+  if (!qr::is_pow2(heads) || !qr::is_pow2(head_dim) || head_dim < 32 || n < 256 || n > 4096)
+    return qr::fail(QR_EUNSUPPORTED, "qr_hadamard_heads_f16: heads = %lld, head_dim = %lld (powers of two, head_dim >= 32, "
+                    "256 <= heads x head_dim <= 4096)", (long long)heads, (long long)head_dim);
+  const uint32_t mask = (uint32_t)((heads - 1) * head_dim);      // the index bits of the heads axis
+  const int rc = qr::launch_hadq_walsh(x, rows, (int)n, n, mask, (float)(1.0 / sqrt((double)heads)), 1.0f, nullptr, nullptr,
+                                       y, n, 0, (cudaStream_t)stream);
+  if (rc == QR_EUNSUPPORTED) return qr::fail(QR_EALIGN, "qr_hadamard_heads_f16: x and y must be 16-byte aligned");
+  return rc;
+}
+
 int qr_hadamard_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx, const void* had_k, int K,
                          float clip, uint8_t* q, void* scales, void* y_out, void* stream) {
   if (ldx < n) return qr::fail(QR_EINVAL, "qr_hadamard_quant_i4: ldx < n");

@@ -4,4 +4,4 @@ from .linear import Linear4bit
 from .normalization import RMSNorm
 from .quantization import Quantizer
 from .hadamard import OnlineHadamard
-from .fused import HadamardQuantizer, fuse_modules
+from .fused import HadamardQuantizer, fuse_modules, HorizontalLinear4bit, fuse_qkv, fuse_gate_up

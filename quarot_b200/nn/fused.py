@@ -112,3 +112,64 @@ class QuantLinear4bit(torch.nn.Module):
                                         self.quantizer.input_clip_ratio)
         return self.linear(self.quantizer(x))
 
+
+
+class HorizontalLinear4bit(torch.nn.Module):
+    """Several Linear4bit modules that read the same quantised input -- q/k/v of an attention block, gate/up of an
+    MLP (e2e/quantized_llama/modeling_llama.py:40-44,108-110: one Quantizer feeds all of them) -- as ONE GEMM.
+
+    The modules' `weight`, `weight_scales` and `bias` are concatenated along the output channels; the modules then
+    hold VIEWS of the concatenated buffers, so nothing is stored twice, `state_dict()` / `load_state_dict()` of the
+    model keep their per-projection keys (`q_proj.weight`, ...) and loading a checkpoint writes straight into the
+    fused operand.  The concatenated buffers are not part of the state dict.  forward returns one tensor per module
+    (column slices of the single [..., sum N] result).  Moving the model to another device afterwards breaks the
+    sharing (torch moves every buffer on its own): fuse after `.to(device)`, or call `refresh()`.
+    """
+
+    def __init__(self, *linears):
+        super().__init__()
+        if len(linears) < 2:
+            raise ValueError("HorizontalLinear4bit: at least two modules")
+        k = linears[0].weight.shape[1]
+        with_bias = [lin.bias is not None for lin in linears]
+        if any(lin.weight.shape[1] != k for lin in linears) or (any(with_bias) and not all(with_bias)):
+            raise ValueError("HorizontalLinear4bit: modules must share in_features and either all or none have a bias")
+        self._linears = list(linears)           # a plain list: the modules stay where they are in the model
+        self.splits = [lin.weight.shape[0] for lin in linears]
+        self.refresh()
+
+    def refresh(self):
+        lins = self._linears
+        self.register_buffer("weight", torch.cat([lin.weight for lin in lins], dim=0), persistent=False)
+        self.register_buffer("weight_scales", torch.cat([lin.weight_scales.view(-1, 1) for lin in lins], dim=0),
+                             persistent=False)
+        if lins[0].bias is not None:
+            self.register_buffer("bias", torch.cat([lin.bias for lin in lins], dim=0), persistent=False)
+        else:
+            self.bias = None
+        start = 0
+        for lin, n in zip(lins, self.splits):
+            lin.weight = self.weight[start:start + n]
+            lin.weight_scales = self.weight_scales[start:start + n]
+            if self.bias is not None:
+                lin.bias = self.bias[start:start + n]
+            start += n
+
+    def forward(self, x):
+        assert type(x) == _ops.PackedQuantizedTensor
+        out = _ops.linear_i4(x.quantized_x, x.scales_x, self.weight, self.weight_scales, self.bias)
+        return out.split(self.splits, dim=-1)
+
+
+def fuse_qkv(attention):
+    """`attention.q_proj / k_proj / v_proj` (Linear4bit) as one GEMM: returns the HorizontalLinear4bit, whose forward
+    gives (q, k, v) for the PackedQuantizedTensor that `attention.quantizer` produced.  State-dict keys are unchanged."""
+    return HorizontalLinear4bit(attention.q_proj, attention.k_proj, attention.v_proj)
+
+
+def fuse_gate_up(mlp, swiglu=False):
+    """`mlp.gate_proj / up_proj` as one GEMM: (gate, up) = fused(x), or, with swiglu=True, a SwiGLULinear4bit whose
+    forward returns act_fn(gate) * up with the product inside the GEMM epilogue.  State-dict keys are unchanged."""
+    if swiglu:
+        return SwiGLULinear4bit(mlp.gate_proj, mlp.up_proj)
+    return HorizontalLinear4bit(mlp.gate_proj, mlp.up_proj)

@@ -92,3 +92,23 @@ def test_converter_state_dict_loads_with_its_key_renames():
     before = set(layer.state_dict())
     assert quarot_b200.nn.fuse_modules(layer) == 1
     assert set(layer.state_dict()) == before
+
+
+def test_horizontal_fusion_keeps_the_checkpoint_keys_and_shares_storage():
+    """fuse_qkv / fuse_gate_up: one concatenated operand, the projections hold views of it, state-dict keys unchanged,
+    and a checkpoint loaded afterwards lands in the fused operand."""
+    layer = _Layer(128, 4, 64, 344)
+    keys = set(layer.state_dict())
+    qkv = quarot_b200.nn.fuse_qkv(layer.self_attn)
+    gu = quarot_b200.nn.fuse_gate_up(layer.mlp)
+    assert set(layer.state_dict()) == keys
+    assert qkv.splits == [128, 64, 64] and qkv.weight.shape == (256, 64) and gu.weight.shape == (688, 64)
+    assert layer.self_attn.k_proj.weight.data_ptr() == qkv.weight[128:192].data_ptr()
+    new = {k: (torch.randint(0, 255, v.shape, dtype=torch.uint8) if v.dtype == torch.uint8 else torch.rand_like(v))
+           for k, v in layer.state_dict().items()}
+    layer.load_state_dict(new)
+    assert torch.equal(qkv.weight, torch.cat([new["self_attn.q_proj.weight"], new["self_attn.k_proj.weight"],
+                                              new["self_attn.v_proj.weight"]]))
+    assert torch.equal(gu.weight_scales, torch.cat([new["mlp.gate_proj.weight_scales"], new["mlp.up_proj.weight_scales"]]))
+    with pytest.raises(ValueError):
+        quarot_b200.nn.HorizontalLinear4bit(layer.self_attn.q_proj)

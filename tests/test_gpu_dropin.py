@@ -66,3 +66,30 @@ def test_upstream_benchmark_script_runs_unmodified(capsys):
         mod.linear4bit_benchmark(argparse.Namespace(bsz=1, seq_len=2048, layer_type=layer_type))
     assert "Int4 time" in capsys.readouterr().out
     assert _lib.kernel_status() == 0
+
+
+def test_fused_qkv_and_gate_up_equal_the_separate_projections():
+    from quarot_b200 import synth
+    hidden, kv, inter, rows = 1024, 256, 2816, 300
+    dev = "cuda:0"
+
+    def lin(i, o, seed):
+        m = quarot_b200.nn.Linear4bit(i, o).to(dev)
+        w, s = synth.weights(o, i, seed=seed)
+        m.weight, m.weight_scales = w.to(dev), s.to(dev)
+        return m
+
+    class Block(torch.nn.Module):
+        pass
+    attn, mlp = Block(), Block()
+    attn.q_proj, attn.k_proj, attn.v_proj = lin(hidden, hidden, 1), lin(hidden, kv, 2), lin(hidden, kv, 3)
+    mlp.gate_proj, mlp.up_proj = lin(hidden, inter, 4), lin(hidden, inter, 5)
+    x = quarot_b200.nn.Quantizer()(synth.activations(rows, hidden, seed=6).to(dev))
+    want = [m(x) for m in (attn.q_proj, attn.k_proj, attn.v_proj, mlp.gate_proj, mlp.up_proj)]
+    q, k, v = quarot_b200.nn.fuse_qkv(attn)(x)
+    g, u = quarot_b200.nn.fuse_gate_up(mlp)(x)
+    for got, ref in zip((q, k, v, g, u), want):
+        assert torch.equal(got, ref)
+    act = quarot_b200.nn.fuse_gate_up(mlp, swiglu=True)(x)
+    assert torch.equal(act, torch.nn.functional.silu(want[3]) * want[4])
+    assert _lib.kernel_status() == 0

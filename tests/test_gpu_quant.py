@@ -252,3 +252,41 @@ def test_rmsnorm_quant_fused(n, rows, clip):
     assert torch.equal(fused.quantized_x.cpu(), q) and torch.equal(q2.cpu(), q)
     assert fused.scales_x.shape == (rows, 1)
 
+
+
+@pytest.mark.parametrize("heads,head_dim", [(32, 128), (8, 128), (16, 64), (64, 64), (64, 128), (2, 128)])
+def test_heads_axis_hadamard_on_the_transposed_view(heads, head_dim):
+    """OnlineHadamard(num_heads) on attn_output.transpose(-1, -2), as the attention block calls it in front of o_proj:
+    transform over the heads axis without a transposed copy where the strided kernel serves the shape (up to 4096
+    values per token), through a contiguous copy otherwise; the result has the strides of the input view."""
+    g = torch.Generator().manual_seed(heads * head_dim)
+    attn = (torch.randn(2, 37, heads, head_dim, generator=g) * 3).half().to(DEV)
+    view = attn.transpose(-1, -2)                      # [2, 37, head_dim, heads], last axis strided
+    y = qb.nn.OnlineHadamard(heads).to(DEV)(view)
+    assert y.shape == view.shape and y.dtype == torch.float16
+    ref = O.hadamard(view.cpu().float().contiguous())
+    ok, worst = _had_close(y.cpu().contiguous(), ref)
+    assert ok, worst
+    back = y.transpose(-1, -2).reshape(2, 37, heads * head_dim)
+    assert back.shape == (2, 37, heads * head_dim)
+    if 256 <= heads * head_dim <= 4096 and head_dim >= 32:
+        assert y.transpose(-1, -2).is_contiguous()      # no copy on the way back either
+
+
+@pytest.mark.parametrize("n,rows", [(256, 7), (512, 3), (1024, 50), (2048, 13), (4096, 29)])
+def test_warp_per_row_walsh_kernel(n, rows):
+    """The register-resident Walsh kernel (tensor-core stage on bits 0, 1, 3, 4, shuffles on bits 5..7) serves whole-row
+    transforms when switched on: Hadamard within 1e-3 of the fp32 operator, scales and codes bit-exact given it."""
+    x = synth.activations(rows, n, seed=n + rows).to(DEV)
+    _lib.set_tuning("hadq_walsh", 1)
+    try:
+        q, s, y = qb.hadamard_quant(x, None, 1, 1.0, return_y=True)
+        y2 = qb.hadamard(x, None, 1)
+    finally:
+        _lib.set_tuning("hadq_walsh", 0)
+    ok, worst = _had_close(y.cpu(), O.hadamard(x.cpu().float()))
+    assert ok, worst
+    assert torch.equal(y, y2)
+    s_ref = O.quantizer_scales(y.cpu())
+    assert torch.equal(s.cpu(), s_ref)
+    assert torch.equal(q.cpu(), O.pack_i4(O.sym_quant_codes(y.cpu(), s_ref)))
