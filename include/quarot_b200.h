@@ -236,6 +236,35 @@ int qr_linear_i4_f16_static(const uint8_t* A, const void* sA, const uint8_t* B, 
                             const void* bias, int64_t M, int64_t N, int64_t K,
                             void* out, int64_t ldo, void* stream);
 
+/* ------------------------------------------------------------- KV cache ---
+ * Paged 4-bit KV cache of the upstream decoder (quarot/transformers/kv_cache.py:130-289).  Layout, as upstream
+ * (quarot/kernels/include/flashinfer/page.cuh:76-103): kv_data [pages, layers, 2 (k | v), heads, page_size, head_dim/2]
+ * uint8, unsigned int4 codes with element 2j in the low nibble of byte j; kv_param [pages, layers, 2, heads,
+ * page_size, 2] fp16 = (scale, zero), value = code * scale - zero.  Sequence b owns the pages
+ * kv_indices[kv_indptr[b] .. kv_indptr[b+1]), the last of which holds last_page_offset[b] tokens (int32 arrays on the
+ * device).  head_dim must be 128, as in the upstream kernels.
+ *
+ * qr_kv_append_i4: [Walsh-Hadamard transform of the keys over head_dim, scale 1/sqrt(head_dim) ->] per-(token, head)
+ * asymmetric int4 quantisation (scale = clamp(max - min, 1e-5) / 15, zero = -min, code = clamp(round((x + zero) /
+ * scale), 0, 15), every step rounded to fp16 as the torch reference does) -> pack -> write into the page slots, for k
+ * and v [tokens, heads, head_dim] fp16.  The page table must already describe the sequences WITH the new tokens;
+ * append_indptr [batch + 1] gives the new tokens per sequence (a prompt), NULL means one token per sequence
+ * (tokens == batch).  One kernel for matmul_had_cuda + asym_quantize_and_pack_i4 (quarot/transformers/kv_cache.py:10-35)
+ * + init_kv_i4 / append_kv_i4 (quarot/kernels/bindings.cpp:140-260, flashinfer/page.cuh:120,167). */
+int qr_kv_append_i4(void* kv_data, void* kv_param, const int32_t* kv_indptr, const int32_t* kv_indices,
+                    const int32_t* last_page_offset, const void* k, const void* v, const int32_t* append_indptr,
+                    int64_t tokens, int batch, int num_layers, int layer, int num_heads, int page_size, int head_dim,
+                    int hadamard_k, void* stream);
+
+/* qr_kv_decode_i4: o[b, h, :] = softmax(q[b, h, :] . K^T / sqrt(head_dim)) V over the cached tokens of sequence b, one
+ * new token per sequence, keys and values dequantised on the fly; q, o [batch, heads, head_dim] fp16.  With
+ * hadamard_q the query is Walsh-Hadamard transformed (and rounded to fp16) first.  Replaces batch_decode_i4
+ * (quarot/kernels/bindings.cpp:115-138, flashinfer/decode.cuh:492) and the query transform of _AttentionStub.forward
+ * (quarot/transformers/kv_cache.py:113-114).  Query heads and KV heads coincide, as upstream. */
+int qr_kv_decode_i4(void* o, const void* q, const void* kv_data, const void* kv_param, const int32_t* kv_indptr,
+                    const int32_t* kv_indices, const int32_t* last_page_offset, int batch, int num_layers, int layer,
+                    int num_heads, int page_size, int head_dim, int hadamard_q, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

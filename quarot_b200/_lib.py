@@ -37,6 +37,8 @@ SIGNATURES = {
     "qr_linear_i4_swiglu_f16": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "qr_rmsnorm_quant_i4": (_int, [_vp, _i64, _i64, _i64, _i64, ctypes.c_float, ctypes.c_float, _vp, _vp, _vp, _vp]),
     "qr_quant_linear_i4_f16": (_int, [_vp, _i64, ctypes.c_float, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
+    "qr_kv_append_i4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _int, _int, _int, _int, _vp]),
+    "qr_kv_decode_i4": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _int, _int, _int, _int, _int, _int, _int, _vp]),
     "qr_linear_workspace_bytes": (ctypes.c_size_t, [_i64, _i64, _i64]),
     "qr_linear_i4_f16_static": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp]),
     "qr_linear_i4_f16_ws": (_int, [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _vp, _i64, _vp, ctypes.c_size_t, _vp]),

@@ -112,8 +112,7 @@ gemv_i4_kernel(const GemvParams p) {
   const int kbytes = p.K >> 1;
   const int nchunks = kbytes >> 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  stage_token_rows<MT, F16, kGemvThreads>(p, smem_a, s_scale, s_red);
-  __syncthreads();
+  pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
 
   // The work of a warp is the flat sequence (channel pair, k step); the weight chunks of step t + 1 are requested
   // before step t is computed, also across pair boundaries, so that every lane always has up to eight 16-byte
@@ -150,7 +149,12 @@ gemv_i4_kernel(const GemvParams p) {
   // rows (more accumulators) the extra registers cost more occupancy than the prefetch gains (measured).
   constexpr bool kPrefetch = (MT <= 2);
   uint4 cur[kGemvRows][2], nxt[kGemvRows][2];
+  // The weights do not depend on the kernel in front: the first chunks are requested before the programmatic-
+  // dependency wait and before the token rows are staged, so that their latency overlaps both.
   if (kPrefetch && total > 0) load_step(0, cur);
+  pdl_wait();   // token rows, scales and the output belong to the preceding kernels
+  stage_token_rows<MT, F16, kGemvThreads>(p, smem_a, s_scale, s_red);
+  __syncthreads();
 #pragma unroll 1
   for (int t = 0; t < total; ++t) {
     if (kPrefetch) {
@@ -240,7 +244,7 @@ static int launch_gemv_mt(const GemvParams& p, cudaStream_t st) {
   int64_t grid = (int64_t)num_sms() * per_sm;
   const int64_t need = ((int64_t)(p.N + kGemvRows - 1) / kGemvRows + (kGemvThreads / 32) - 1) / (kGemvThreads / 32);
   if (grid > need) grid = need;
-  QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGemvThreads), smem, st, false, p));
+  QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGemvThreads), smem, st, false, p));   // measured: no gain from a programmatic launch here
   return QR_OK;
 }
 

@@ -125,3 +125,18 @@ def test_swiglu_is_the_fp16_product_of_torch():
     u = (torch.randn(64, 256, generator=gen) * 3).half()
     assert torch.equal(O.swiglu_fp16(g, u), torch.nn.functional.silu(g) * u)
 
+
+
+def test_kv_cache_quantisation_bit_exact_vs_upstream():
+    """The 4-bit KV-cache format: the oracle's restatement of asym_quantize_and_pack_i4 / unpack_i4_and_asym_dequantize
+    against outputs of the upstream helpers (tests/golden/make_golden_kv.py)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "kv_cache.npz"))
+    for name in ("gauss", "outlier", "tiny", "const", "ties"):
+        x = torch.from_numpy(g[name + "_x"])
+        q, scale, zero = O.kv_asym_quant_pack(x)
+        assert np.array_equal(q.numpy(), g[name + "_q"]), name
+        assert np.array_equal(scale.numpy().view(np.uint16), g[name + "_scale"].view(np.uint16)), name
+        assert np.array_equal(zero.numpy().view(np.uint16), g[name + "_zero"].view(np.uint16)), name
+        deq = O.kv_unpack_dequant(q, scale, zero)
+        assert np.array_equal(deq.numpy().view(np.uint16), g[name + "_deq"].view(np.uint16)), name

@@ -111,7 +111,14 @@ def test_module_surface_and_state_dict_contract():
     ref = (x.float() * torch.rsqrt(x.float().pow(2).mean(-1, keepdim=True) + 1e-5)).half()
     assert torch.equal(rms(x), ref)
     with pytest.raises(NotImplementedError):
-        quarot_b200.transformers.MultiLayerPagedKVCache4Bit()
+        quarot_b200.transformers.MultiLayerPagedKVCache4Bit(1, 16, 64, "cpu", 1, 2, 128, disable_quant=True)
+    cache = quarot_b200.transformers.MultiLayerPagedKVCache4Bit(2, 16, 100, "cpu", 3, 4, 128)
+    assert cache.pages.shape == (14, 3, 2, 4, 16, 64) and cache.pages.dtype == torch.uint8
+    assert cache.scales.shape == (14, 3, 2, 4, 16, 2) and cache.get_seq_length() == 0 and cache.to_legacy_cache() is cache
+    cache.length = 33
+    specs = cache.get_cache_specs_for_flash_infer(None)
+    assert specs["kv_indptr"].tolist() == [0, 3, 6] and specs["kv_indices"].tolist() == [0, 2, 4, 1, 3, 5]
+    assert specs["last_page_offset"].tolist() == [1, 1]
 
 
 def test_ops_reject_cpu_tensors():
