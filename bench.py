@@ -367,7 +367,7 @@ def roofline_record(layers, M, res, peaks, peak_src, workload, int8_probe, regio
         nbytes = sum(bytes_gemm(M, K, N) + (2.0 * M * K - M * K / 2.0 if (fused and not had) else 0.0)
                      for (_, K, N, had) in layers)
         achieved = nbytes / (res["gemm_ms"] * 1e-3) / 1e9
-        rec = {"bound": "hbm", "kernel": "decode_mma_kernel / gemm_i4_kernel<swap> (one launch per linear)",
+        rec = {"bound": "hbm", "kernel": ("gemv_i4_kernel" if M <= 4 else "gemm_i4_decode_kernel") + " (one launch per linear)",
                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peak_src,
                "algorithmic_bytes_per_step": nbytes, "kernel_ms_per_step": res["gemm_ms"],
@@ -662,6 +662,93 @@ def heads_hadamard_run(dev, steps, warmup):
     return {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "shape": [1, M, heads, hd], "launch_mode": "eager"}
 
 
+# --profile-case NAME: the launches one kernel summary under profiles/ was captured from.  Every case runs its kernel
+# a few times on inputs larger than L2 where the kernel streams from HBM, and nothing else of the benchmark.
+PROFILE_CASES = {
+    # name: (kind, M, K, N or Kronecker factor)
+    "gemm_qkv": ("linear", 2048, 4096, 12288),
+    "gemm_o": ("linear", 2048, 4096, 4096),
+    "gemm_gate_up": ("linear", 2048, 4096, 22016),
+    "gemm_down": ("linear", 2048, 11008, 4096),
+    "decode16_qkv": ("linear", 16, 4096, 12288),
+    "decode16_down": ("linear", 16, 11008, 4096),
+    "decode64_down": ("linear", 64, 11008, 4096),
+    "gemv1_qkv": ("linear", 1, 4096, 12288),
+    "quant_4096": ("hadq", 2048, 4096, 0),
+    "walsh_4096": ("hadq", 2048, 4096, 1),
+    "had_172x64": ("hadq", 2048, 11008, 172),
+    "had_28x1024": ("hadq", 1024, 28672, 28),
+    "heads_axis": ("heads", 2048, 4096, 32),
+    "kv_decode": ("kv", 16, 2048, 32),
+}
+
+
+def profile_case(name, dev, reps=3):
+    import quarot_b200 as qb
+    from quarot_b200 import synth, _lib
+    from quarot_b200.functional import hadamard as FH
+    kind, M, K, N = PROFILE_CASES[name]
+    if kind == "linear":
+        x = synth.activations_device(M, K, device=dev)
+        w, sw = synth.weights_device(N, K, device=dev)
+        q, sx, _ = qb.hadamard_quant(x, None, 0, 1.0)
+        fn = lambda: qb.linear_i4(q, sx, w, sw.view(-1))
+    elif kind == "hadq":
+        x = synth.activations_device(M, K, device=dev)
+        table = FH.device_table(N, dev) if N > 1 else None
+        fn = lambda: qb.hadamard_quant(x, table, N, 1.0)
+    elif kind == "heads":
+        x = torch.randn(M, N, K // N, device=dev, dtype=torch.float16)
+        had = qb.nn.OnlineHadamard(N)
+        fn = lambda: had(x.transpose(-1, -2))
+    else:
+        cache, attend, qv = kv_decode_setup(dev, batch=M, seq=K, heads=N)
+        fn = lambda: attend(qv)
+    for _ in range(reps):
+        fn()
+    torch.cuda.synchronize(dev)
+    if _lib.kernel_status() != 0:
+        raise SystemExit("bench.py: kernel status %d" % _lib.kernel_status())
+    print(json.dumps({"profile_case": name, "launch_groups": reps}))
+
+
+def kv_decode_setup(dev, batch, seq, heads, page=16):
+    """A paged 4-bit KV cache of `batch` sequences of `seq` tokens (one layer, head_dim 128, keys Hadamard-
+    transformed), and the attention callable for one new token per sequence."""
+    from quarot_b200.transformers import MultiLayerPagedKVCache4Bit
+    g = torch.Generator().manual_seed(7)
+    cache = MultiLayerPagedKVCache4Bit(batch, page, seq + 8, dev, 1, heads, 128, hadamard_dtype=torch.float16)
+    k = (torch.randn(batch, seq, heads, 128, generator=g) * 2.0).half().to(dev)
+    v = (torch.randn(batch, seq, heads, 128, generator=g) * 2.0).half().to(dev)
+    cache.update(k, v, 0, {})
+    k1 = (torch.randn(batch, 1, heads, 128, generator=g) * 2.0).half().to(dev)
+    v1 = (torch.randn(batch, 1, heads, 128, generator=g) * 2.0).half().to(dev)
+    attend = cache.update(k1, v1, 0, {})
+    qv = (torch.randn(batch, 1, heads, 128, generator=g) * 1.5).half().to(dev)
+    return cache, attend, qv
+
+
+def kv_decode_run(dev, steps, warmup, batch=16, seq=2048, heads=32):
+    """Decode attention over the paged 4-bit cache (the row after the linears): one new token per sequence against
+    `seq` cached tokens; algorithmic bytes = packed K and V codes plus their (scale, zero) pairs, read once."""
+    cache, attend, qv = kv_decode_setup(dev, batch, seq, heads)
+    for _ in range(max(warmup, 3)):
+        attend(qv)
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        attend(qv)
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / steps
+    tokens = batch * (seq + 1)
+    nbytes = tokens * heads * 2 * (64 + 4)
+    return {"ms_per_step": ms, "batch": batch, "cached_tokens": seq + 1, "heads": heads, "page_size": 16,
+            "algorithmic_bytes": nbytes, "achieved_gbs": nbytes / (ms * 1e-3) / 1e9,
+            "note": "eager launches; the %.1f MB of pages exceed the 126 MB L2" % (nbytes / 1e6)}
+
+
 def other_configs(qb, dev, dist, world, rank, peaks, peak_src, headline_workload, int8_probe):
     """Short device-timed runs of the benchmark configurations that are not the headline."""
     out = {}
@@ -694,6 +781,10 @@ def other_configs(qb, dev, dist, world, rank, peaks, peak_src, headline_workload
         out["heads_axis_hadamard_n32"] = heads_hadamard_run(dev, 30, 5)
     except Exception as exc:
         out["heads_axis_hadamard_n32"] = {"skipped": repr(exc)}
+    try:
+        out["kv_cache_decode_attention"] = kv_decode_run(dev, 30, 5)
+    except Exception as exc:
+        out["kv_cache_decode_attention"] = {"skipped": repr(exc)}
     if world > 1:
         # strong scaling of the 70B layer: the 4096 token rows are split over the ranks
         layers = LAYERS["LLAMA2_70B"]
@@ -727,6 +818,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA-graph replays")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="skip other_configs, the sustained run and the parity block")
+    ap.add_argument("--profile-case", default="", choices=[""] + sorted(PROFILE_CASES),
+                    help="run one kernel case a few times and exit (the command the ncu summaries under profiles/ name)")
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
@@ -777,6 +870,9 @@ def main():
         raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    if args.profile_case:
+        profile_case(args.profile_case, dev)
+        return 0
     dist = None
     if world > 1:
         import torch.distributed as dist
