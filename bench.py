@@ -70,9 +70,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 NOMINAL_INT8_TOPS = 4500.0
 DECODE_MAX_M = 128      # workloads with at most this many token rows are reported against the HBM roofline
 
-# DRAM traffic per launch of the dominant kernel, from ncu captures (dram__bytes_read.sum + dram__bytes_write.sum);
-# the capture behind every entry is summarised in profiles/.  Key: (workload, tokens per GPU).
-NCU_TRAFFIC_BYTES = {}
+# DRAM traffic of the dominant kernel's launches of one step, from ncu captures (dram__bytes_read.sum +
+# dram__bytes_write.sum of one launch per linear; the captures are summarised under profiles/).
+# Key: (workload, tokens per GPU).  7B prefill: qkv 29.46 + 6.26 MB, o_proj 12.66 + 0, gate/up 49.46 + 44.87,
+# down 33.90 + 0.34 -- below the algorithmic bytes because most of the fp16 output is still in L2 when a launch ends.
+NCU_TRAFFIC_BYTES = {("llama2_7b_prefill", 2048): 176.95e6}
 
 
 def load_peaks():
@@ -389,8 +391,10 @@ def roofline_record(layers, M, res, peaks, peak_src, workload, int8_probe, regio
                "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
                "peak_exceeded": bool(achieved > peak),
                "kernel_ms_per_step": res["gemm_ms"]}
-    traffic = NCU_TRAFFIC_BYTES.get((workload, M))
-    rec["traffic"] = traffic
+    rec["traffic"] = NCU_TRAFFIC_BYTES.get((workload, M))
+    if rec["traffic"] is not None:
+        rec["traffic_note"] = "ncu dram bytes read + written by the step's launches of this kernel (one capture per linear)"
+        rec["algorithmic_bytes_per_step"] = float(sum(bytes_gemm(M, K, N) for (_, K, N, _) in layers))
     return rec
 
 
