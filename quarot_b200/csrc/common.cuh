@@ -32,7 +32,7 @@ struct Tuning {
   int pdl = 2;                // programmatic dependent launch: 0 never, 1 always, 2 decode-sized launches only
   int hadq_path = 0;          // 1 = always the generic Hadamard kernel (A/B checks)
   int hadq_walsh = 0;         // 1: warp-per-row register kernel also for whole-row Walsh transforms of 256 .. 4096 (measured slower)
-  int hadq_tc = 1;            // tensor-core kernel for n = 64 K Kronecker shapes
+  int hadq_tc = 1;            // tensor-core kernel for n = 64 K Kronecker shapes: 1 above 128 rows, 2 always, 0 never
 };
 extern Tuning g_tuning;
 // programmatic dependent launch for a launch that works on `rows` token rows?

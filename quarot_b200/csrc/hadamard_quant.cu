@@ -678,7 +678,8 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
                           use_pdl(p.rows), p));
     return QR_OK;
   }
-  if (base_ok && K > 1 && m == 64 && ldx == n && g_tuning.hadq_tc != 0) {
+  // (below 129 rows the persistent tensor-core kernel's set-up is not amortised: 7.2 against 6.4 us at 8 rows of 11008)
+  if (base_ok && K > 1 && m == 64 && ldx == n && (rows > 128 || g_tuning.hadq_tc == 2) && g_tuning.hadq_tc != 0) {
     const int rc = launch_hadq_tc(x, rows, n, K, had_k, clip, q, scales, y_out, do_quant, st);
     if (rc != QR_EUNSUPPORTED) return rc;
   }

@@ -17,6 +17,15 @@ def _bits(t):
     return t.detach().cpu().contiguous().view(torch.int16)
 
 
+@pytest.fixture(params=["auto", "tcgen05"], autouse=True)
+def kronecker_kernel_choice(request):
+    """Shapes n = 64 K go to the per-row kernel up to 128 rows and to the persistent tcgen05 kernel above; the small,
+    ragged row counts of this module run once with that rule and once with the tcgen05 kernel forced."""
+    _lib.set_tuning("hadq_tc", 2 if request.param == "tcgen05" else 1)
+    yield
+    _lib.set_tuning("hadq_tc", 1)
+
+
 def test_sym_quant_matches_upstream_fixtures(golden):
     g = golden["quantizer"]
     for t in sorted(k[:-2] for k in g.files if k.endswith("_x")):
