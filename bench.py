@@ -425,7 +425,7 @@ def e2e_run(qb, layers, M, dev, steps, warmup, work):
     """Same step through the module API with HOST buffers: per linear, activations are copied
     from pinned host memory, pushed through Sequential([HadamardQuantizer|Quantizer], Linear4bit)
     and the fp16 result is copied back to pinned host memory.  Copies run on their own streams
-    so that transfers of neighbouring linears overlap the kernels."""
+    so that transfers of neighbouring linears and of neighbouring steps overlap the kernels and each other."""
     mods, hx, hout = [], [], []
     for L in work:
         lin = qb.nn.Linear4bit(L["K"], L["N"]).to(dev)
@@ -461,9 +461,9 @@ def e2e_run(qb, layers, M, dev, steps, warmup, work):
             with torch.cuda.stream(s_out):
                 hout[i].copy_(out, non_blocking=True)
                 out.record_stream(s_out)
-        fin = torch.cuda.Event()
-        fin.record(s_out)
-        main.wait_event(fin)
+        # no join here: the copy-out of this step overlaps the copy-in and the kernels of the next one (the host link
+        # is full duplex); inputs are safe because the next copy-in waits for an event recorded behind this step's
+        # kernels, outputs because the copy-out stream keeps its order
 
     def copies_only(which):
         """The step's host copies alone, one direction at a time: what the host link gives this rank."""
@@ -488,6 +488,7 @@ def e2e_run(qb, layers, M, dev, steps, warmup, work):
     e0.record(main)
     for _ in range(steps):
         step()
+    main.wait_stream(s_out)          # the timed region ends when the last result has reached the host
     e1.record(main)
     torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1) / steps
