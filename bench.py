@@ -369,7 +369,7 @@ def roofline_record(layers, M, res, peaks, peak_src, workload, int8_probe, regio
         nbytes = sum(bytes_gemm(M, K, N) + (2.0 * M * K - M * K / 2.0 if (fused and not had) else 0.0)
                      for (_, K, N, had) in layers)
         achieved = nbytes / (res["gemm_ms"] * 1e-3) / 1e9
-        rec = {"bound": "hbm", "kernel": ("gemv_i4_kernel" if M <= 4 else "gemm_i4_decode_kernel") + " (one launch per linear)",
+        rec = {"bound": "hbm", "kernel": ("gemv_mma_i4_kernel" if M <= 32 else "gemm_i4_decode_kernel") + " (one launch per linear)",
                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peak_src,
                "algorithmic_bytes_per_step": nbytes, "kernel_ms_per_step": res["gemm_ms"],

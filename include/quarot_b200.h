@@ -54,8 +54,8 @@ const char* qr_last_error(void);
 int qr_kernel_status(int* status_out);
 
 /* Kernel-selection knobs, process-wide: "gemm_bn", "gemm_bn2", "gemm_pst", "gemm_grid", "gemm_decode_max_m",
- * "gemm_decode", "gemm_splitk", "gemm_2sm", "gemm_tma_out", "gemv_max_m", "pdl", "hadq_path", "hadq_tc",
- * "hadq_walsh".  Every setting computes the same results; the defaults are the measured best choices.  Unknown keys
+ * "gemm_decode", "gemm_splitk", "gemm_2sm", "gemm_tma_out", "gemv_max_m", "gemv_mma_max_m", "pdl", "hadq_path",
+ * "hadq_tc", "hadq_walsh".  Every setting computes the same results; the defaults are the measured best choices.  Unknown keys
  * return QR_EINVAL.  No upstream counterpart. */
 int qr_set_tuning(const char* key, int value);
 
@@ -192,7 +192,10 @@ int qr_quant_linear_i4_f16(const void* x, int64_t ldx, float clip, const uint8_t
                            const void* bias, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
                            void* stream);
 
-/* Decode-sized M (M <= 64) is bound by streaming the weights, so every SM has to stream its share.  Wide layers
+/* Decode-sized M (M <= 64) is bound by streaming the weights, so every SM has to stream its share.  Up to 32 token
+ * rows a kernel without scratch does that (weights from global memory straight into warp-level MMAs), as long as the
+ * token rows fit into shared memory (K up to about 54 000 / 26 000 / 12 000 values for up to 8 / 16 / 32 rows).  What is
+ * left -- 33 to 64 rows, or longer rows -- runs on a tcgen05 kernel.  There wide layers
  * get there by dealing the weight rows out to the SMs, which needs no scratch.  A narrow layer (at most 48 weight rows
  * per SM, e.g. N = 4096) would leave most of every 128-row MMA idle that way; its (128-row tile, k stage) units are
  * dealt out instead, a tile may then be shared by several CTAs, and its pieces meet in a caller-provided scratch
@@ -225,7 +228,8 @@ int qr_linear_i4_f16_ws(const uint8_t* A, const void* sA, const uint8_t* B, cons
  *   - shapes whose scratch (qr_linear_workspace_bytes: 64 KiB of counters + 128 x BN x 4 bytes per tile of 128
  *     output channels, BN = 16 / 32 / 64 for up to 16 / 32 / 64 token rows) exceeds that size are refused with
  *     QR_EUNSUPPORTED and a message: N <= 4096 fits at every M <= 64, N <= 7104 at M <= 32; shapes that need no
- *     scratch (wide layers, prefill sizes, a handful of rows) are simply run;
+ *     scratch (wide layers, prefill sizes, and up to 32 token rows whose length the scratch-free kernel takes) are
+ *     simply run;
  *   - the first call on each device looks up the array's device address (once per device, with
  *     that device current); make that first call before any stream capture begins;
  *   - all calls share the one array and find the previous call's contents in it; the entry point

@@ -14,7 +14,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_DIR = os.path.join(HERE, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libquarot_b200.so")
-SOURCES = ["api.cu", "quant.cu", "hadamard_quant.cu", "hadamard_tc.cu", "hadamard_walsh.cu", "gemm_i4.cu", "gemm_i4_decode.cu", "gemv_i4.cu", "kv_cache.cu"]
+SOURCES = ["api.cu", "quant.cu", "hadamard_quant.cu", "hadamard_tc.cu", "hadamard_walsh.cu", "gemm_i4.cu", "gemm_i4_decode.cu", "gemv_i4.cu", "gemv_mma_i4.cu", "kv_cache.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-std=c++17", "-lineinfo",

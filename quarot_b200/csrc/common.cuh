@@ -27,7 +27,8 @@ struct Tuning {
   int gemm_splitk = 1;        // decode, narrow layers: deal out (tile, stage) units when a workspace is given
   int gemm_2sm = 1;           // prefill: 2-CTA kernel (cta_group::2) instead of the 1-CTA kernel
   int gemm_tma_out = 1;       // 2-CTA kernel: tiled TMA stores of the output where alignment allows
-  int gemv_max_m = 4;         // token rows up to which the weight-streaming CUDA-core kernel is used
+  int gemv_max_m = 0;         // token rows up to which the weight-streaming CUDA-core (dp4a) kernel is used (it also serves the quantiser-fused call)
+  int gemv_mma_max_m = 32;    // token rows up to which the weight-streaming mma.sync kernel is used (0: never)
   int gemm_decode = 1;        // decode: the weight-streaming tcgen05 kernel (0: tokens on the MMA rows as at prefill)
   int pdl = 2;                // programmatic dependent launch: 0 never, 1 always, 2 decode-sized launches only
   int hadq_path = 0;          // 1 = always the generic Hadamard kernel (A/B checks)

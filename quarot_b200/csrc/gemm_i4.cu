@@ -980,6 +980,10 @@ int launch_gemm_i4_decode(const uint8_t* X, const uint8_t* W, int64_t M, int64_t
                           const void* sX, const void* sW, const void* bias, bool f16, int grid_cap, void* ws, size_t ws_bytes,
                           cudaStream_t st);
 size_t decode_stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
+// weight-streaming mma.sync kernel for M <= 32 (gemv_mma_i4.cu)
+bool gemv_mma_serves(int64_t M, int64_t K);
+int launch_gemv_mma_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                       const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st);
 // weight-streaming CUDA-core kernel for M <= 8 (gemv_i4.cu)
 int launch_gemv_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
                    const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st,
@@ -1074,6 +1078,11 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
       rc = launch_gemv_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
       if (rc != QR_EUNSUPPORTED) return rc;
     }
+    // a few more rows: the same streaming structure with warp-level MMAs (gemv_mma_i4.cu)
+    if (M <= g_tuning.gemv_mma_max_m) {
+      rc = launch_gemv_mma_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
+      if (rc != QR_EUNSUPPORTED) return rc;
+    }
     // decode-sized M on the tensor cores: weights on the MMA rows, all SMs streaming (gemm_i4_decode.cu)
     if (g_tuning.gemm_decode != 0) {
       rc = launch_gemm_i4_decode(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, grid_cap, ws, ws_bytes, st);
@@ -1132,6 +1141,7 @@ int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, 
 // SMs and pieces of a tile meet in scratch memory); everything else runs without scratch.
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= qr::g_tuning.gemv_max_m || M > qr::g_tuning.gemm_decode_max_m || qr::g_tuning.gemm_decode == 0) return 0;
+  if (M <= qr::g_tuning.gemv_mma_max_m && qr::gemv_mma_serves(M, K)) return 0;      // the mma.sync GEMV needs no scratch
   return qr::decode_stream_workspace_bytes(M, N, K);
 }
 

@@ -1,0 +1,227 @@
+// Kernel (b) for 1 .. 32 token rows: the weight-streaming GEMV with warp-level tensor-core MMAs.
+//
+// With this few token rows the layer is one pass over the packed weights, and what the tcgen05 kernel of
+// gemm_i4_decode.cu pays per launch (tensor-memory allocation, TMA ring fill, an MMA instruction of 100+ cycles per
+// 32 K values and 128 weight rows) is more than the pass itself.  The CUDA-core GEMV of gemv_i4.cu has none of that
+// but runs out of dp4a throughput above four rows.  This kernel keeps its structure -- weights from global memory
+// straight into registers, widened there, token rows packed in shared memory -- and replaces dp4a by
+// mma.sync.m16n8k32.s8 (measured on this GPU: one per 8 cycles and scheduler, 2048 MACs per cycle and SM; the
+// pass needs a fifth of that at memory speed).
+//
+// Mapping.  A warp owns 16 output channels (weight rows n0 .. n0 + 15).  In the m16n8k32 A fragment lane (g, t),
+// g = lane / 4, t = lane % 4, holds rows g and g + 8 and, of each, eight of the 32 k values as two int8x4 registers.
+// Which k values a register holds is free as long as the B fragment follows the same rule, so lane (g, t) simply
+// loads the t-th 16-byte chunk of a 64-byte piece of its two weight rows, and word j of that chunk, widened with the
+// x16 trick of the other kernels ((w << 4) & 0xF0F0F0F0 = the even nibbles, w & 0xF0F0F0F0 = the odd ones, as int8
+// with a factor 16), is the register pair of MMA j: one 16-byte load per row feeds four MMAs.  The B fragment of
+// lane (g, t) is token row g at the same chunk and word: one 16-byte shared-memory load per four MMAs (token rows are
+// padded by 64 bytes so that the eight rows of a quarter-warp fall into different banks).  Further B fragments
+// serve token rows 8 .. 15 and 16 .. 31.  The accumulators are 256 x the dot products, as everywhere else, and the epilogue is
+// the arithmetic of the other forms of kernel (b): bit-identical results.
+//
+// Parallelism and balance.  One or two persistent CTAs of eight warps per SM; the weight rows are dealt out to the
+// CTAs as contiguous ranges of N / CTAs rows (any number: every SM streams the same number of bytes), a CTA walks
+// its range in groups of 16 rows (rows of the last group beyond the range are not loaded and their accumulators are
+// not stored), and its eight warps split the K range of every group eight ways; their partial fragments meet in
+// shared memory behind one barrier per group (two alternating areas), after which all threads add up and store one
+// element each.  Every lane keeps the loads of the next four 64-byte pieces of its two rows in flight while it
+// computes the current four, also across groups.
+#include "common.cuh"
+
+namespace qr {
+
+struct GemvMmaParams {
+  const uint8_t* A;      // [M, K/2] packed token rows
+  const uint8_t* B;      // [N, K/2] packed weights
+  const __half* sA;      // [M] or null (int32 mode)
+  const __half* sB;      // [N] or null
+  const __half* bias;    // [N] or null
+  void* out;             // [M, N] fp16 (ldo) or int32
+  int64_t ldo;
+  int M, N, K;
+  int a_stride;          // bytes between token rows in shared memory (K / 2 + 64)
+};
+
+constexpr int kGmWarps = 8;
+constexpr int kGmThreads = 32 * kGmWarps;
+constexpr int kGmUnroll = 4;       // 64-byte pieces per row and loop iteration
+
+__device__ __forceinline__ uint4 gm_ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NF: fragments of eight token rows (1: M <= 8, 2: M <= 16, 4: M <= 32)
+template <int NF, bool F16>
+__global__ void __launch_bounds__(kGmThreads, 2)
+gemv_mma_i4_kernel(const GemvMmaParams p) {
+  constexpr int MT = 8 * NF;
+  constexpr int kFrag = NF * 4 * 32;                           // ints of one warp's accumulator fragments
+  extern __shared__ __align__(16) unsigned char gm_smem[];     // MT padded token rows, then two reduction areas
+  __shared__ float s_scale[MT];
+  const int kbytes = p.K >> 1;
+  const int nchunks = kbytes >> 4;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
+
+  // this CTA's rows, this warp's slice of K (a multiple of the four chunks a warp takes per row and step)
+  const int row_begin = (int)((long long)blockIdx.x * p.N / gridDim.x);
+  const int row_end = (int)((long long)(blockIdx.x + 1) * p.N / gridDim.x);
+  const int cps = (((nchunks + kGmWarps - 1) / kGmWarps) + 3) & ~3;
+  const int c_begin = warp * cps;
+  const int c_end = (c_begin + cps < nchunks) ? c_begin + cps : nchunks;
+  const int steps = c_begin < c_end ? (c_end - c_begin + 3) >> 2 : 0;
+  const int iters = (steps + kGmUnroll - 1) / kGmUnroll;
+
+  auto load_iter = [&](int rb, int it, uint4 (&w)[kGmUnroll][2]) {
+    const int r0 = rb + g, r1 = r0 + 8;
+    const uint8_t* p0 = p.B + (size_t)r0 * kbytes;
+    const uint8_t* p1 = p.B + (size_t)r1 * kbytes;
+#pragma unroll
+    for (int u = 0; u < kGmUnroll; ++u) {
+      const int c = c_begin + ((it * kGmUnroll + u) << 2) + t;
+      const bool ok = c < c_end;
+      w[u][0] = (ok && r0 < row_end) ? gm_ld_stream16(p0 + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+      w[u][1] = (ok && r1 < row_end) ? gm_ld_stream16(p1 + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+    }
+  };
+
+  uint4 cur[kGmUnroll][2], nxt[kGmUnroll][2];
+  // The weights do not depend on the kernel in front: the first chunks are requested before the programmatic-
+  // dependency wait and before the token rows are staged.
+  if (row_begin < row_end && iters > 0) load_iter(row_begin, 0, cur);
+  pdl_wait();   // token rows, scales and the output belong to the preceding kernels
+  for (int i = threadIdx.x; i < MT * nchunks; i += kGmThreads) {
+    const int m = i / nchunks, c = i - m * nchunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m < p.M) v = *reinterpret_cast<const uint4*>(p.A + (size_t)m * kbytes + (size_t)c * 16);
+    *reinterpret_cast<uint4*>(gm_smem + (size_t)m * p.a_stride + (size_t)c * 16) = v;
+  }
+  if (F16 && threadIdx.x < MT) s_scale[threadIdx.x] = threadIdx.x < p.M ? __half2float(p.sA[threadIdx.x]) : 0.0f;
+  __syncthreads();
+  int* red = reinterpret_cast<int*>(gm_smem + (size_t)MT * p.a_stride);       // [2][warp][kFrag]
+
+  int parity = 0;
+  for (int rb = row_begin; rb < row_end; rb += 16, parity ^= 1) {
+    int acc[NF][4];
+#pragma unroll
+    for (int f = 0; f < NF; ++f)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[f][e] = 0;
+#pragma unroll 1
+    for (int it = 0; it < iters; ++it) {
+      // the next iteration's chunks (of this group, or the first of the next group) are requested before this
+      // iteration is computed
+      if (it + 1 < iters) load_iter(rb, it + 1, nxt);
+      else if (rb + 16 < row_end) load_iter(rb + 16, 0, nxt);
+#pragma unroll
+      for (int u = 0; u < kGmUnroll; ++u) {
+        const int c = c_begin + ((it * kGmUnroll + u) << 2) + t;
+        const uint32_t w0[4] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w};
+        const uint32_t w1[4] = {cur[u][1].x, cur[u][1].y, cur[u][1].z, cur[u][1].w};
+#pragma unroll
+        for (int f = 0; f < NF; ++f) {
+          // chunks at or beyond c_end meet zero weights; the address stays inside the padded token row
+          const int cc = c < nchunks ? c : 0;
+          const uint4 xa = *reinterpret_cast<const uint4*>(gm_smem + (size_t)(8 * f + g) * p.a_stride + (size_t)cc * 16);
+          const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            mma_s8_16832(acc[f], (w0[j] << 4) & 0xF0F0F0F0u, (w1[j] << 4) & 0xF0F0F0F0u, w0[j] & 0xF0F0F0F0u, w1[j] & 0xF0F0F0F0u,
+                         (xw[j] << 4) & 0xF0F0F0F0u, xw[j] & 0xF0F0F0F0u);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kGmUnroll; ++u) { cur[u][0] = nxt[u][0]; cur[u][1] = nxt[u][1]; }
+    }
+    // the eight partial fragments meet in shared memory; the areas alternate, so one barrier per group is enough
+    int* area = red + parity * (kGmWarps * kFrag);
+#pragma unroll
+    for (int f = 0; f < NF; ++f)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) area[warp * kFrag + (f * 4 + e) * 32 + lane] = acc[f][e];
+    __syncthreads();
+    // thread i finishes element i: fragment f, register e, lane l -> channel rb + l / 4 + 8 (e / 2), token 8 f + 2 (l % 4) + e % 2
+    for (int i = threadIdx.x; i < kFrag; i += kGmThreads) {
+      int v = 0;
+#pragma unroll
+      for (int w2 = 0; w2 < kGmWarps; ++w2) v += area[w2 * kFrag + i];
+      const int l = i & 31, e = (i >> 5) & 3, f = i >> 7;
+      const int n = rb + (l >> 2) + ((e >> 1) << 3);
+      const int tok = 8 * f + 2 * (l & 3) + (e & 1);
+      if (n < row_end && tok < p.M) {
+        v >>= 8;       // the widened operands carry a factor 16 each
+        if (F16) {
+          __half o = __float2half_rn((float)v * (s_scale[tok] * __half2float(p.sB[n])));
+          if (p.bias) o = __hadd(o, p.bias[n]);
+          reinterpret_cast<__half*>(p.out)[(size_t)tok * p.ldo + n] = o;
+        } else {
+          reinterpret_cast<int32_t*>(p.out)[(size_t)tok * p.ldo + n] = v;
+        }
+      }
+    }
+  }
+}
+
+// Shared memory of a CTA: the padded token rows and two reduction areas.
+static size_t gemv_mma_smem(int nf, int64_t K) {
+  return (size_t)(8 * nf) * (size_t)((K >> 1) + 64) + (size_t)2 * kGmWarps * nf * 4 * 32 * sizeof(int);
+}
+constexpr size_t kGmSmemMax = 220 * 1024;
+
+// Does this kernel take M token rows of K values?  (The token rows have to fit into shared memory.)
+bool gemv_mma_serves(int64_t M, int64_t K) {
+  if (M < 1 || M > 32 || K < 32 || K % 32 != 0 || K > 65536) return false;
+  return gemv_mma_smem(M <= 8 ? 1 : (M <= 16 ? 2 : 4), K) <= kGmSmemMax;
+}
+
+template <int NF, bool F16>
+static int launch_gemv_mma_nf(GemvMmaParams& p, cudaStream_t st) {
+  p.a_stride = (p.K >> 1) + 64;
+  const size_t smem = gemv_mma_smem(NF, p.K);
+  if (smem > kGmSmemMax) return QR_EUNSUPPORTED;
+  auto kern = gemv_mma_i4_kernel<NF, F16>;
+  static thread_local size_t configured[64] = {0};
+  int dev = 0;
+  QR_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev >= 64 || configured[dev] < smem)) {
+    QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = smem;
+  }
+  const int per_sm = (2 * (smem + 1024) <= 226 * 1024) ? 2 : 1;
+  int64_t grid = (int64_t)num_sms() * per_sm;
+  const int64_t need = ((int64_t)p.N + 15) / 16;
+  if (grid > need) grid = need;
+  QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGmThreads), smem, st, use_pdl(p.M), p));
+  return QR_OK;
+}
+
+// Returns QR_EUNSUPPORTED when the shape is not one this kernel serves (the caller then takes another path).
+int launch_gemv_mma_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
+                       const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st) {
+  if (!gemv_mma_serves(M, K) || N < 1 || N > (1 << 30)) return QR_EUNSUPPORTED;
+  if (!aligned16(A) || !aligned16(B)) return QR_EUNSUPPORTED;
+  GemvMmaParams p;
+  p.A = A; p.B = B; p.sA = reinterpret_cast<const __half*>(sA); p.sB = reinterpret_cast<const __half*>(sB);
+  p.bias = reinterpret_cast<const __half*>(bias); p.out = out; p.ldo = ldo;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.a_stride = 0;
+  if (f16) {
+    if (M <= 8) return launch_gemv_mma_nf<1, true>(p, st);
+    if (M <= 16) return launch_gemv_mma_nf<2, true>(p, st);
+    return launch_gemv_mma_nf<4, true>(p, st);
+  }
+  if (M <= 8) return launch_gemv_mma_nf<1, false>(p, st);
+  if (M <= 16) return launch_gemv_mma_nf<2, false>(p, st);
+  return launch_gemv_mma_nf<4, false>(p, st);
+}
+
+}  // namespace qr

@@ -218,6 +218,17 @@ def test_full_size_config0_properties():
     assert _lib.kernel_status() == 0
 
 
+@pytest.fixture
+def tcgen05_decode_kernel():
+    """At most 32 token rows go to the mma.sync weight-streaming kernel by default; these tests are about the tcgen05
+    decode kernel behind it (33 .. 64 rows, or rows of more values than fit into shared memory), so they switch the
+    other one off."""
+    _lib.set_tuning("gemv_mma_max_m", 0)
+    yield
+    _lib.set_tuning("gemv_mma_max_m", 32)
+
+
+@pytest.mark.usefixtures("tcgen05_decode_kernel")
 @pytest.mark.parametrize("M,N,K", [(5, 4096, 4096), (8, 4096, 4096), (32, 4096, 11008), (24, 4096, 4096),
                                    (17, 1000, 2048), (32, 512, 28672), (64, 7000, 1024)])
 def test_decode_unit_split_matches_row_split(M, N, K):
@@ -243,21 +254,21 @@ def test_decode_unit_split_matches_row_split(M, N, K):
         assert torch.equal(qb.linear_i4(ad, sxd, wd, swd, bd), one)
     finally:
         _lib.set_tuning("gemm_decode", 1)
-        _lib.set_tuning("gemv_max_m", 4)
+        _lib.set_tuning("gemv_max_m", 0)
     assert _lib.kernel_status() == 0
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (2, 1000, 2048), (3, 12288, 4096), (5, 4096, 11008), (8, 22016, 4096),
                                    (7, 33, 64), (8, 8192, 28672), (1, 1, 64)])
 def test_weight_streaming_kernel_for_a_few_rows(M, N, K):
-    """M <= 8 on the CUDA-core kernel (it serves up to four rows by default; gemv_max_m = 8 sends all of these shapes
-    to it): one pass over the packed weights with dp4a; exact accumulators and the same dequantisation arithmetic as
+    """M <= 8 on the CUDA-core kernel (by default it serves only the quantiser-fused call; gemv_max_m = 8 sends all of
+    these shapes to it): one pass over the packed weights with dp4a; exact accumulators and the same dequantisation arithmetic as
     the tensor-core kernels."""
     _lib.set_tuning("gemv_max_m", 8)
     try:
         _weight_streaming_case(M, N, K)
     finally:
-        _lib.set_tuning("gemv_max_m", 4)
+        _lib.set_tuning("gemv_max_m", 0)
 
 
 def _weight_streaming_case(M, N, K):
@@ -276,6 +287,7 @@ def _weight_streaming_case(M, N, K):
     assert _lib.kernel_status() == 0
 
 
+@pytest.mark.usefixtures("tcgen05_decode_kernel")
 def test_workspace_argument_errors():
     a, w = _rand_packed(16, 4096, 1).to(DEV), _rand_packed(4096, 4096, 2).to(DEV)
     sx, sw = torch.ones(16, device=DEV).half(), torch.ones(4096, device=DEV).half()
@@ -287,9 +299,14 @@ def test_workspace_argument_errors():
     assert rc == -1 and "workspace" in _lib.last_error() and need > 256
     assert _lib.lib.qr_linear_workspace_bytes(2048, 4096, 4096) == 0     # prefill shapes need no scratch
     assert _lib.lib.qr_linear_workspace_bytes(16, 12288, 4096) == 0      # nor do wide layers at decode sizes
-    assert _lib.lib.qr_linear_workspace_bytes(2, 4096, 4096) == 0        # nor the CUDA-core kernel
+    _lib.set_tuning("gemv_mma_max_m", 32)                                 # the default: up to 32 rows without scratch
+    assert _lib.lib.qr_linear_workspace_bytes(2, 4096, 4096) == 0
+    assert _lib.lib.qr_linear_workspace_bytes(32, 4096, 4096) == 0
+    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 4096) > 0
+    assert _lib.lib.qr_linear_workspace_bytes(32, 4096, 28672) > 0       # rows too long for that kernel's shared memory
 
 
+@pytest.mark.usefixtures("tcgen05_decode_kernel")
 def test_one_workspace_serves_calls_of_different_shapes():
     """Decode calls of different shapes share the cached workspace; every call leaves its counters at zero and
     partial tiles never land in the counter region, whatever the order of the shapes (more tiles after fewer)."""
@@ -398,6 +415,45 @@ def test_quantizer_inside_the_weight_streaming_kernel(M, N, K, clip):
 
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (5, 12288, 4096), (8, 4096, 11008), (16, 22016, 4096), (13, 1000, 2048),
+                                   (9, 33, 1024), (16, 7, 4096), (12, 300, 1088), (7, 4096, 64), (16, 130, 320),
+                                   (11, 5000, 1152), (16, 17, 192), (2, 64, 20480)])
+def test_weight_streaming_kernel_with_warp_level_mmas(M, N, K):
+    """5 .. 16 token rows (here also fewer, with the CUDA-core kernel switched off): weights straight from global
+    memory into the A fragments of mma.sync.m16n8k32.s8, K split over the warps of a CTA on narrow layers.  Exact
+    int32 accumulators, the epilogue arithmetic of the other kernels, ragged N and K, an output pitch that is not a
+    multiple of anything, repeated launches, with and without programmatic dependent launch."""
+    g = torch.Generator().manual_seed(M * 41 + N)
+    a, w = _rand_packed(M, K, 91), _rand_packed(N, K, 92)
+    sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand(N, generator=g) * 0.015 + 0.005).half()
+    bias = (torch.randn(N, generator=g) * 0.5).half()
+    acc = O.matmul_i4(a, w)
+    ref = O.sym_dequant_fp32(acc, sx, sw).half()
+    ad, wd = a.to(DEV), w.to(DEV)
+    _lib.set_tuning("gemv_max_m", 0)
+    try:
+        for pdl in (0, 1):
+            _lib.set_tuning("pdl", pdl)
+            assert torch.equal(qb.matmul(ad, wd).cpu(), acc)
+            out = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), bias.to(DEV))
+            assert torch.equal(out.cpu(), ref + bias)
+            wide = torch.full((M, N + 3), 7.0, dtype=torch.float16, device=DEV)
+            for _ in range(2):
+                qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), out=wide[:, :N])
+                assert torch.equal(wide[:, :N].cpu(), ref)
+            assert bool((wide[:, N:] == 7.0).all())
+        # the tcgen05 decode kernel gives the same bits
+        _lib.set_tuning("gemv_mma_max_m", 0)
+        assert torch.equal(qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV)).cpu(), ref)
+    finally:
+        _lib.set_tuning("gemv_max_m", 0)
+        _lib.set_tuning("gemv_mma_max_m", 32)
+        _lib.set_tuning("pdl", 2)
+    assert _lib.kernel_status() == 0
+
+
+@pytest.mark.usefixtures("tcgen05_decode_kernel")
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (3, 12288, 4096), (5, 4096, 11008), (8, 22016, 4096), (16, 4096, 4096),
                                    (13, 1000, 2048), (16, 8192, 28672), (9, 33, 1024), (16, 7, 4096), (12, 300, 1088), (32, 4096, 4096), (64, 22016, 4096), (40, 4096, 11008), (33, 1000, 256), (64, 130, 320),
                                    (16, 20000, 1024)])
@@ -427,6 +483,6 @@ def test_weight_streaming_tensor_core_kernel(M, N, K):
             out3 = qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), use_workspace=False)
             assert torch.equal(out3.cpu(), O.sym_dequant_fp32(acc, sx, sw).half())
     finally:
-        _lib.set_tuning("gemv_max_m", 4)
+        _lib.set_tuning("gemv_max_m", 0)
         _lib.set_tuning("pdl", 2)
     assert _lib.kernel_status() == 0

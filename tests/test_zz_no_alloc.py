@@ -44,10 +44,12 @@ def _call(fn, a, sa, w, sw, bias, M, N, K):
     return out
 
 
-@pytest.mark.parametrize("M,N,K", [(16, 4096, 4096), (32, 4096, 4096), (64, 4096, 11008)])
+@pytest.mark.parametrize("M,N,K", [(40, 4096, 4096), (48, 4096, 4096), (64, 4096, 11008), (24, 4096, 28672)])
 def test_static_scratch_entry_matches_ordinary_entry_twice(M, N, K):
     lib = _lib.lib
-    assert 0 < lib.qr_linear_workspace_bytes(M, N, K) <= LIMIT           # these shapes do use the array
+    # these shapes do use the array: 33 .. 64 token rows on a narrow layer, or rows too long for the kernel that serves
+    # fewer token rows without scratch
+    assert 0 < lib.qr_linear_workspace_bytes(M, N, K) <= LIMIT
     first = _inputs(M, N, K, seed=1)
     second = _inputs(M, N, K, seed=2)
     for args in (first, second):                                        # two calls in a row share the array
@@ -59,7 +61,7 @@ def test_static_scratch_entry_matches_ordinary_entry_twice(M, N, K):
 
 def test_static_scratch_entry_calls_of_different_shapes_share_the_array_and_allocate_nothing():
     lib = _lib.lib
-    shapes = [(64, 4096, 4096), (16, 1000, 2048), (32, 4096, 11008), (16, 1000, 2048), (64, 4096, 4096)]
+    shapes = [(64, 4096, 4096), (40, 1000, 2048), (16, 4096, 4096), (48, 4096, 11008), (40, 1000, 2048), (64, 4096, 4096)]
     cases = [(_inputs(M, N, K, seed=5 + i), (M, N, K)) for i, (M, N, K) in enumerate(shapes)]
     wants = [_call(lib.qr_linear_i4_f16, *args, *shape) for (args, shape) in cases]
     _call(lib.qr_linear_i4_f16_static, *cases[0][0], *cases[0][1])       # first call on the device: address look-up
