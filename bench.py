@@ -369,7 +369,8 @@ def roofline_record(layers, M, res, peaks, peak_src, workload, int8_probe, regio
         nbytes = sum(bytes_gemm(M, K, N) + (2.0 * M * K - M * K / 2.0 if (fused and not had) else 0.0)
                      for (_, K, N, had) in layers)
         achieved = nbytes / (res["gemm_ms"] * 1e-3) / 1e9
-        rec = {"bound": "hbm", "kernel": ("gemv_mma_i4_kernel" if M <= 32 else "gemm_i4_decode_kernel") + " (one launch per linear)",
+        rec = {"bound": "hbm", "kernel": ("gemv_i4_kernel with the quantiser inside (three linears) and gemv_mma_i4_kernel (down)" if fused else
+                          "gemv_mma_i4_kernel" if M <= 32 else "gemm_i4_decode_kernel") + ", one launch per linear",
                "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                "peak_source": "hbm_gbs of MEASURED_PEAKS.json (%s)" % peak_src,
                "algorithmic_bytes_per_step": nbytes, "kernel_ms_per_step": res["gemm_ms"],
@@ -675,10 +676,13 @@ PROFILE_CASES = {
     "gemm_o": ("linear", 2048, 4096, 4096),
     "gemm_gate_up": ("linear", 2048, 4096, 22016),
     "gemm_down": ("linear", 2048, 11008, 4096),
-    "decode16_qkv": ("linear", 16, 4096, 12288),
+    "decode1_qkv": ("linear", 1, 4096, 12288),            # mma.sync weight-streaming kernel
+    "decode8_qkv": ("linear", 8, 4096, 12288),
     "decode16_down": ("linear", 16, 11008, 4096),
-    "decode64_down": ("linear", 64, 11008, 4096),
-    "gemv1_qkv": ("linear", 1, 4096, 12288),
+    "decode32_gate_up": ("linear", 32, 4096, 22016),
+    "decode64_qkv": ("linear", 64, 4096, 12288),          # tcgen05 decode kernel, row split
+    "decode64_down": ("linear", 64, 11008, 4096),         # tcgen05 decode kernel, unit split
+    "decode1_quant_qkv": ("quant_linear", 1, 4096, 12288),  # CUDA-core kernel with the quantiser inside
     "quant_4096": ("hadq", 2048, 4096, 0),
     "walsh_4096": ("hadq", 2048, 4096, 1),
     "had_172x64": ("hadq", 2048, 11008, 172),
@@ -698,6 +702,10 @@ def profile_case(name, dev, reps=3):
         w, sw = synth.weights_device(N, K, device=dev)
         q, sx, _ = qb.hadamard_quant(x, None, 0, 1.0)
         fn = lambda: qb.linear_i4(q, sx, w, sw.view(-1))
+    elif kind == "quant_linear":
+        x = synth.activations_device(M, K, device=dev)
+        w, sw = synth.weights_device(N, K, device=dev)
+        fn = lambda: qb.quant_linear_i4(x, w, sw.view(-1))
     elif kind == "hadq":
         x = synth.activations_device(M, K, device=dev)
         table = FH.device_table(N, dev) if N > 1 else None

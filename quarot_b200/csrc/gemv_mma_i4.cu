@@ -199,7 +199,8 @@ static int launch_gemv_mma_nf(GemvMmaParams& p, cudaStream_t st) {
   }
   const int per_sm = (2 * (smem + 1024) <= 226 * 1024) ? 2 : 1;
   int64_t grid = (int64_t)num_sms() * per_sm;
-  const int64_t need = ((int64_t)p.N + 15) / 16;
+  // every CTA gets N / grid rows, so all SMs stream the same number of bytes; only very small N shrinks the grid
+  const int64_t need = ((int64_t)p.N + 7) / 8;
   if (grid > need) grid = need;
   QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGmThreads), smem, st, use_pdl(p.M), p));
   return QR_OK;
