@@ -311,7 +311,6 @@ template <int KT>
 __global__ void __launch_bounds__(hadq_max_threads(KT), hadq_min_blocks(KT))
 hadq_fast_kernel(const HadqParams p) {
   pdl_launch_dependents();
-  pdl_wait();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int tid = threadIdx.x;
   const int nthreads = blockDim.x;
@@ -350,6 +349,8 @@ hadq_fast_kernel(const HadqParams p) {
       }
     }
   }
+  // the table does not depend on the kernel in front, the activations do: its fragments were requested above
+  pdl_wait();
 
   int parity = 0;
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
