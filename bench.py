@@ -819,6 +819,28 @@ def other_configs(qb, dev, dist, world, rank, peaks, peak_src, headline_workload
     return out
 
 
+_RESULT_FD = None
+
+
+def keep_stdout_for_the_result():
+    """Libraries below (the collective library's version banner, for one) write to file descriptor 1; the contract is
+    ONE JSON line on stdout.  Everything but that line goes to stderr from here on."""
+    global _RESULT_FD
+    if _RESULT_FD is None:
+        sys.stdout.flush()
+        _RESULT_FD = os.dup(1)
+        os.dup2(2, 1)
+
+
+def emit(line):
+    text = json.dumps(line) + "\n"
+    if _RESULT_FD is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text.encode())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -834,6 +856,7 @@ def main():
     ap.add_argument("--profile-case", default="", choices=[""] + sorted(PROFILE_CASES),
                     help="run one kernel case a few times and exit (the command the ncu summaries under profiles/ name)")
     args = ap.parse_args()
+    keep_stdout_for_the_result()
     if args.warmup < 3 and args.impl == "ours":
         args.warmup = 3
 
@@ -867,7 +890,7 @@ def main():
             c0 = cpu_reference_run(LAYERS["CONFIG0"], 2048, 1, 0, rows=2048)
             line["config0_in_full"] = {"ms_per_step": c0["ms_per_step_sample"], "value": c0["value"], "unit": "TOPS",
                                        "tokens": 2048, "cores": c0["cores"]}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     # ------------------------------------------------------------ our arm (GPU)
@@ -901,7 +924,7 @@ def main():
                 "data": "synthetic", "config": {"workload": args.workload, "tokens_per_gpu": M, "hidden": K,
                                                 "l2": "inputs rotate over 12 buffers (201 MB)"},
                 "modules_unfused": {"ms_per_step": res["unfused_ms"]}, "gpu_launches": args.steps}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     if args.workload.endswith("_mlp_swiglu"):
@@ -918,7 +941,7 @@ def main():
                 "product_as_separate_kernels": {"ms_per_step": res["unfused_ms"],
                                                 "value": ops / (res["unfused_ms"] * 1e-3) / 1e12, "unit": "TOPS"},
                 "tokens_per_s": M / (ms * 1e-3), "gpu_launches": 4 * args.steps}
-        print(json.dumps(line))
+        emit(line)
         return 0
 
     if args.workload == "llama2_70b_mlp_colsplit":
@@ -941,7 +964,7 @@ def main():
         if dist is not None and not args.no_others:
             line["parity"] = multi_gpu_parity(dev, world, rank, dist)
         if rank == 0:
-            print(json.dumps(line))
+            emit(line)
         if dist is not None:
             dist.destroy_process_group()
         return 0
@@ -1019,7 +1042,7 @@ def main():
         r = cpu_reference_run(layers, M, 2, 1, budget_s=12.0)
         line["cpu_baseline"] = {k: r[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     if dist is not None:
         dist.destroy_process_group()
     return 0

@@ -645,7 +645,10 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0 && row0 < p.rowsP) {
-            for (int g = 0; g < p.n_outs; ++g) tma_store_2d(&tmOs.m[g], stg_u32, tq * (kBN2 / 2) + c0, row0);
+            // the destinations are visited in an order that differs from warp to warp and tile to tile, so that the
+            // ranks of a column split do not all write to the same peer at the same time
+            for (int i = 0, g = (int)((tl + warp) % (uint32_t)p.n_outs); i < p.n_outs; ++i, g = (g + 1 == p.n_outs) ? 0 : g + 1)
+              tma_store_2d(&tmOs.m[g], stg_u32, tq * (kBN2 / 2) + c0, row0);
             bulk_commit_group();
           }
         }
@@ -706,7 +709,10 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           if (lane == 0 && row0 < p.rowsP && tq * bn + c0 < p.rowsQ) {
             // one tiled store per destination: the block goes to this GPU's output and, in a column split, straight
             // into the peers' copies of the full matrix over NVLink
-            for (int g = 0; g < p.n_outs; ++g) tma_store_2d(&tmOs.m[g], stg_u32, tq * bn + c0, row0);
+            // into the peers' copies of the full matrix over NVLink; the destinations are visited in an order that differs
+            // from warp to warp and tile to tile, so that the ranks do not all write to the same peer at the same time
+            for (int i = 0, g = (int)((tl + warp) % (uint32_t)p.n_outs); i < p.n_outs; ++i, g = (g + 1 == p.n_outs) ? 0 : g + 1)
+              tma_store_2d(&tmOs.m[g], stg_u32, tq * bn + c0, row0);
             bulk_commit_group();
           }
         }

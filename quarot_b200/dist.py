@@ -138,8 +138,11 @@ class FusedColumnSplitLinear4bit(ColumnSplitLinear4bit):
         rows = x.quantized_x.numel() // x.quantized_x.shape[-1]
         target.barrier()          # nobody still reads the previous contents
         if rows > 128:
+            # destinations start with this rank's own copy and go round the ring: the kernel visits them in an order that
+            # depends on the tile and the warp only, so at any moment the ranks write to different peers
+            ptrs = target.ptrs[self.rank:] + target.ptrs[:self.rank]
             _ops.linear_i4_outs(x.quantized_x, x.scales_x, self.weight, self.weight_scales, self.bias,
-                                [p + col_bytes for p in target.ptrs], target.cols)
+                                [p + col_bytes for p in ptrs], target.cols)
         else:
             # few token rows (served by the decode kernels): the slab is computed locally and copied into the
             # column block of every rank's matrix
