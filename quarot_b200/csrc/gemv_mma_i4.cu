@@ -117,6 +117,20 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
     for (int f = 0; f < NF; ++f)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[f][e] = 0;
+    // channel scale and bias of the elements this thread will finish: requested now, needed behind the barrier
+    constexpr int kFin = (kFrag + kGmThreads - 1) / kGmThreads;
+    float fin_scale[kFin];
+    __half fin_bias[kFin];
+    if (F16) {
+#pragma unroll
+      for (int q = 0; q < kFin; ++q) {
+        const int i = threadIdx.x + q * kGmThreads;
+        const int n = rb + ((i & 31) >> 2) + ((((i >> 5) & 3) >> 1) << 3);
+        const bool live = i < kFrag && n < row_end;
+        fin_scale[q] = live ? __half2float(__ldg(p.sB + n)) : 0.0f;
+        fin_bias[q] = (live && p.bias) ? __ldg(p.bias + n) : __float2half(0.0f);
+      }
+    }
 #pragma unroll 1
     for (int it = 0; it < iters; ++it) {
       // the next iteration's chunks (of this group, or the first of the next group) are requested before this
@@ -128,16 +142,22 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
         const int c = c_begin + ((it * kGmUnroll + u) << 2) + t;
         const uint32_t w0[4] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w};
         const uint32_t w1[4] = {cur[u][1].x, cur[u][1].y, cur[u][1].z, cur[u][1].w};
+        // chunks at or beyond c_end meet zero weights; the address stays inside the padded token row
+        const int cc = c < nchunks ? c : 0;
+        uint4 xa[NF];
 #pragma unroll
-        for (int f = 0; f < NF; ++f) {
-          // chunks at or beyond c_end meet zero weights; the address stays inside the padded token row
-          const int cc = c < nchunks ? c : 0;
-          const uint4 xa = *reinterpret_cast<const uint4*>(gm_smem + (size_t)(8 * f + g) * p.a_stride + (size_t)cc * 16);
-          const uint32_t xw[4] = {xa.x, xa.y, xa.z, xa.w};
+        for (int f = 0; f < NF; ++f)
+          xa[f] = *reinterpret_cast<const uint4*>(gm_smem + (size_t)(8 * f + g) * p.a_stride + (size_t)cc * 16);
+        // word j of the chunks feeds MMA j of every fragment; consecutive MMAs go to different accumulators
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            mma_s8_16832(acc[f], (w0[j] << 4) & 0xF0F0F0F0u, (w1[j] << 4) & 0xF0F0F0F0u, w0[j] & 0xF0F0F0F0u, w1[j] & 0xF0F0F0F0u,
-                         (xw[j] << 4) & 0xF0F0F0F0u, xw[j] & 0xF0F0F0F0u);
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t a0 = (w0[j] << 4) & 0xF0F0F0F0u, a1 = (w1[j] << 4) & 0xF0F0F0F0u;
+          const uint32_t a2 = w0[j] & 0xF0F0F0F0u, a3 = w1[j] & 0xF0F0F0F0u;
+#pragma unroll
+          for (int f = 0; f < NF; ++f) {
+            const uint32_t xw = j == 0 ? xa[f].x : j == 1 ? xa[f].y : j == 2 ? xa[f].z : xa[f].w;
+            mma_s8_16832(acc[f], a0, a1, a2, a3, (xw << 4) & 0xF0F0F0F0u, xw & 0xF0F0F0F0u);
+          }
         }
       }
 #pragma unroll
@@ -151,7 +171,10 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
       for (int e = 0; e < 4; ++e) area[warp * kFrag + (f * 4 + e) * 32 + lane] = acc[f][e];
     __syncthreads();
     // thread i finishes element i: fragment f, register e, lane l -> channel rb + l / 4 + 8 (e / 2), token 8 f + 2 (l % 4) + e % 2
-    for (int i = threadIdx.x; i < kFrag; i += kGmThreads) {
+#pragma unroll
+    for (int q = 0; q < kFin; ++q) {
+      const int i = threadIdx.x + q * kGmThreads;
+      if (i >= kFrag) break;
       int v = 0;
 #pragma unroll
       for (int w2 = 0; w2 < kGmWarps; ++w2) v += area[w2 * kFrag + i];
@@ -161,8 +184,8 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
       if (n < row_end && tok < p.M) {
         v >>= 8;       // the widened operands carry a factor 16 each
         if (F16) {
-          __half o = __float2half_rn((float)v * (s_scale[tok] * __half2float(p.sB[n])));
-          if (p.bias) o = __hadd(o, p.bias[n]);
+          __half o = __float2half_rn((float)v * (s_scale[tok] * fin_scale[q]));
+          if (p.bias) o = __hadd(o, fin_bias[q]);
           reinterpret_cast<__half*>(p.out)[(size_t)tok * p.ldo + n] = o;
         } else {
           reinterpret_cast<int32_t*>(p.out)[(size_t)tok * p.ldo + n] = v;
