@@ -144,9 +144,34 @@ struct KvDecodeParams {
   const int32_t* last_page_offset;
   int batch, layers, layer, heads, page_size;
   int hadamard_q;
+  int splits;                   // CTAs (one cluster) that share the tokens of a (sequence, head): 1, 2, 4 or 8
 };
 
 constexpr int kKvDecWarps = 8;
+
+__device__ __forceinline__ uint32_t kv_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void kv_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a float of CTA `rank` of the cluster at the same shared-memory address as `local` here
+__device__ __forceinline__ float kv_peer_float(const float* local, uint32_t rank) {
+  uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local)), peer;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+  return v;
+}
+
+// Byte `k` (0 .. 3) of `bytes`, a value below 256, as a float without an integer-to-float conversion (those issue at a
+// quarter of the rate of ordinary arithmetic): 0x4B0000vv is 2^23 + vv exactly.
+template <int k>
+__device__ __forceinline__ float byte_to_float(uint32_t bytes) {
+  return __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7440 + k)) - 8388608.0f;
+}
 
 __global__ void __launch_bounds__(32 * kKvDecWarps)
 kv_decode_kernel(const KvDecodeParams p) {
@@ -154,8 +179,11 @@ kv_decode_kernel(const KvDecodeParams p) {
   __shared__ float s_qsum;
   __shared__ float s_m[kKvDecWarps], s_l[kKvDecWarps];
   __shared__ __align__(16) float s_o[kKvDecWarps][kHeadDim];
+  __shared__ float s_part[2 + kHeadDim];          // this CTA's share when a cluster splits the sequence: m, l, o[128]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.x / p.heads, head = blockIdx.x % p.heads;
+  const int item = blockIdx.x / p.splits;
+  const int b = item / p.heads, head = item % p.heads;
+  const uint32_t crank = p.splits > 1 ? kv_cluster_rank() : 0u;
   const int first = p.indptr[b];
   const long long seq_len = (long long)(p.indptr[b + 1] - first - 1) * p.page_size + p.last_page_offset[b];
 
@@ -181,9 +209,14 @@ kv_decode_kernel(const KvDecodeParams p) {
   float m = -INFINITY, l = 0.0f, zacc = 0.0f;
   float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   const size_t rows_per_page_kv = (size_t)p.heads * p.page_size;      // rows between the k and the v block of a page
-  for (long long base = (long long)warp * 32; base < seq_len; base += 32 * kKvDecWarps) {
+  // the CTAs of a cluster take contiguous ranges of whole 32-token chunks
+  const long long chunks = (seq_len + 31) >> 5;
+  const long long per = ((chunks + p.splits - 1) / p.splits) << 5;
+  const long long tok_begin = (long long)crank * per;
+  const long long tok_end = (tok_begin + per < seq_len) ? tok_begin + per : seq_len;
+  for (long long base = tok_begin + (long long)warp * 32; base < tok_end; base += 32 * kKvDecWarps) {
     const long long t = base + lane;
-    const bool valid = t < seq_len;
+    const bool valid = t < tok_end;
     size_t krow = 0;
     float score = -INFINITY, vs = 0.0f, vz = 0.0f;
     if (valid) {
@@ -201,15 +234,16 @@ kv_decode_kernel(const KvDecodeParams p) {
           // word i of chunk c holds elements 32 c + 8 i .. + 7, element e in bits [4e, 4e + 4)
           const float4 q0 = *reinterpret_cast<const float4*>(s_q + 32 * c + 8 * i);
           const float4 q1 = *reinterpret_cast<const float4*>(s_q + 32 * c + 8 * i + 4);
-          const uint32_t u = ww[i];
-          dot = fmaf(q0.x, (float)(u & 15u), dot);
-          dot = fmaf(q0.y, (float)((u >> 4) & 15u), dot);
-          dot = fmaf(q0.z, (float)((u >> 8) & 15u), dot);
-          dot = fmaf(q0.w, (float)((u >> 12) & 15u), dot);
-          dot = fmaf(q1.x, (float)((u >> 16) & 15u), dot);
-          dot = fmaf(q1.y, (float)((u >> 20) & 15u), dot);
-          dot = fmaf(q1.z, (float)((u >> 24) & 15u), dot);
-          dot = fmaf(q1.w, (float)(u >> 28), dot);
+          // even elements are the low nibbles of the four bytes, odd elements the high nibbles
+          const uint32_t ev = ww[i] & 0x0F0F0F0Fu, od = (ww[i] >> 4) & 0x0F0F0F0Fu;
+          dot = fmaf(q0.x, byte_to_float<0>(ev), dot);
+          dot = fmaf(q0.y, byte_to_float<0>(od), dot);
+          dot = fmaf(q0.z, byte_to_float<1>(ev), dot);
+          dot = fmaf(q0.w, byte_to_float<1>(od), dot);
+          dot = fmaf(q1.x, byte_to_float<2>(ev), dot);
+          dot = fmaf(q1.y, byte_to_float<2>(od), dot);
+          dot = fmaf(q1.z, byte_to_float<3>(ev), dot);
+          dot = fmaf(q1.w, byte_to_float<3>(od), dot);
         }
       }
       const float2 kpar = __half22float2(p.param[krow]);
@@ -237,17 +271,30 @@ kv_decode_kernel(const KvDecodeParams p) {
     // values: lane = head dimensions 4 lane .. 4 lane + 3; token tt of the chunk broadcasts p * scale and its row
     const float ps = pr * vs;
     const size_t vrow = krow + rows_per_page_kv;
-    const int ntok = (int)((seq_len - base) < 32 ? (seq_len - base) : 32);
-    for (int tt = 0; tt < ntok; ++tt) {
-      const float w = __shfl_sync(0xffffffffu, ps, tt);
-      const uint32_t rlo = __shfl_sync(0xffffffffu, (uint32_t)vrow, tt);
-      const uint32_t rhi = __shfl_sync(0xffffffffu, (uint32_t)(vrow >> 32), tt);
-      const size_t r = ((size_t)rhi << 32) | rlo;
-      const uint32_t c = __ldg(reinterpret_cast<const uint16_t*>(p.data + r * (kHeadDim / 2) + 2 * lane));
-      o[0] = fmaf(w, (float)(c & 15u), o[0]);
-      o[1] = fmaf(w, (float)((c >> 4) & 15u), o[1]);
-      o[2] = fmaf(w, (float)((c >> 8) & 15u), o[2]);
-      o[3] = fmaf(w, (float)(c >> 12), o[3]);
+    const int ntok = (int)((tok_end - base) < 32 ? (tok_end - base) : 32);
+    // eight tokens at a time: their loads are all requested before the first is used (one 2-byte load per token and
+    // lane would otherwise wait for memory 32 times per chunk)
+#pragma unroll 1
+    for (int t0 = 0; t0 < ntok; t0 += 8) {
+      float wv[8];
+      uint32_t cv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int tt = t0 + u;                       // tokens beyond the sequence carry weight 0 and the row of a valid one
+        wv[u] = __shfl_sync(0xffffffffu, ps, tt & 31);
+        const uint32_t rlo = __shfl_sync(0xffffffffu, (uint32_t)vrow, tt & 31);
+        const uint32_t rhi = __shfl_sync(0xffffffffu, (uint32_t)(vrow >> 32), tt & 31);
+        const size_t r = ((size_t)rhi << 32) | rlo;
+        cv[u] = __ldg(reinterpret_cast<const uint16_t*>(p.data + r * (kHeadDim / 2) + 2 * lane));
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const uint32_t ev = cv[u] & 0x0F0Fu, od = (cv[u] >> 4) & 0x0F0Fu;
+        o[0] = fmaf(wv[u], byte_to_float<0>(ev), o[0]);
+        o[1] = fmaf(wv[u], byte_to_float<0>(od), o[1]);
+        o[2] = fmaf(wv[u], byte_to_float<1>(ev), o[2]);
+        o[3] = fmaf(wv[u], byte_to_float<1>(od), o[3]);
+      }
     }
   }
   // the zero points are the same for every head dimension
@@ -268,6 +315,13 @@ kv_decode_kernel(const KvDecodeParams p) {
       const float4 v = *reinterpret_cast<const float4*>(&s_o[w][4 * lane]);
       acc[0] = fmaf(v.x, f, acc[0]); acc[1] = fmaf(v.y, f, acc[1]); acc[2] = fmaf(v.z, f, acc[2]); acc[3] = fmaf(v.w, f, acc[3]);
     }
+    if (p.splits > 1) {
+      // publish this CTA's share; the first CTA of the cluster merges them below
+      if (lane == 0) { s_part[0] = mm; s_part[1] = ll; }
+      s_part[2 + 4 * lane + 0] = acc[0]; s_part[2 + 4 * lane + 1] = acc[1];
+      s_part[2 + 4 * lane + 2] = acc[2]; s_part[2 + 4 * lane + 3] = acc[3];
+    }
+    if (p.splits == 1) {
     const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;       // an empty sequence gives zeros
     const __half2 h0 = __floats2half2_rn(acc[0] * inv, acc[1] * inv);
     const __half2 h1 = __floats2half2_rn(acc[2] * inv, acc[3] * inv);
@@ -275,6 +329,30 @@ kv_decode_kernel(const KvDecodeParams p) {
     out.x = *reinterpret_cast<const uint32_t*>(&h0);
     out.y = *reinterpret_cast<const uint32_t*>(&h1);
     *reinterpret_cast<uint2*>(p.o + ((size_t)b * p.heads + head) * kHeadDim + 4 * lane) = out;
+    }
+  }
+  if (p.splits > 1) {
+    kv_cluster_sync();                        // every share of the cluster is in shared memory
+    if (crank == 0 && warp == 0) {
+      float mm = -INFINITY;
+      for (int r = 0; r < p.splits; ++r) mm = fmaxf(mm, kv_peer_float(&s_part[0], (uint32_t)r));
+      float ll = 0.0f, acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (int r = 0; r < p.splits; ++r) {
+        const float mr = kv_peer_float(&s_part[0], (uint32_t)r);
+        const float f = (mr == -INFINITY) ? 0.0f : exp2f(mr - mm);
+        ll += kv_peer_float(&s_part[1], (uint32_t)r) * f;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(kv_peer_float(&s_part[2 + 4 * lane + e], (uint32_t)r), f, acc[e]);
+      }
+      const float inv = ll > 0.0f ? 1.0f / ll : 0.0f;       // an empty sequence gives zeros
+      const __half2 h0 = __floats2half2_rn(acc[0] * inv, acc[1] * inv);
+      const __half2 h1 = __floats2half2_rn(acc[2] * inv, acc[3] * inv);
+      uint2 out;
+      out.x = *reinterpret_cast<const uint32_t*>(&h0);
+      out.y = *reinterpret_cast<const uint32_t*>(&h1);
+      *reinterpret_cast<uint2*>(p.o + ((size_t)b * p.heads + head) * kHeadDim + 4 * lane) = out;
+    }
+    kv_cluster_sync();                        // nobody leaves while its shared memory may still be read
   }
 }
 
@@ -328,8 +406,24 @@ int qr_kv_decode_i4(void* o, const void* q, const void* kv_data, const void* kv_
   p.indptr = kv_indptr; p.indices = kv_indices; p.last_page_offset = last_page_offset;
   p.batch = batch; p.layers = num_layers; p.layer = layer; p.heads = num_heads; p.page_size = page_size;
   p.hadamard_q = hadamard_q;
-  qr::kv_decode_kernel<<<(unsigned)(batch * num_heads), 32 * qr::kKvDecWarps, 0, (cudaStream_t)stream>>>(p);
-  QR_LAUNCH_CHECK("kv_decode_kernel");
+  // few (sequence, head) pairs: a cluster of 2, 4 or 8 CTAs shares the tokens of each, so that about three CTAs per SM
+  // have work; their shares are merged through distributed shared memory
+  const long long items = (long long)batch * num_heads;
+  int splits = 1;
+  while (splits < 8 && items * splits * 2 <= 3ll * qr::num_sms()) splits *= 2;
+  p.splits = splits;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)splits;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3((unsigned)(items * splits));
+  cfg.blockDim = dim3(32 * qr::kKvDecWarps);
+  cfg.stream = (cudaStream_t)stream;
+  cfg.attrs = attr;
+  cfg.numAttrs = splits > 1 ? 1 : 0;
+  QR_CUDA(cudaLaunchKernelEx(&cfg, qr::kv_decode_kernel, p));
   return QR_OK;
 }
 
