@@ -170,30 +170,36 @@ __device__ __forceinline__ float scale_from_absmax(float a, float clip, __half* 
 // 16-byte chunks t, t + T, t + 2T, t + 3T of the row (coalesced), keeps them in registers across
 // the row-wide absmax reduction and stores 4 packed bytes per chunk.  The next row's loads are
 // issued before the current row is reduced.
-__global__ void __launch_bounds__(1024)
+// CPT = 16-byte chunks per thread; PF = request the next row before the current one is reduced (persistent CTAs that
+// walk several rows) -- without it and with eight chunks per thread a CTA is small enough that every row of a
+// prefill-sized call is resident at once.
+template <int CPT, bool PF>
+__global__ void __launch_bounds__(PF ? 1024 : 512)
 quant_rows_kernel(const HadqParams p) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float red[2][32];
   const int tid = threadIdx.x, T = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = T >> 5;
   const int nchunks = p.n >> 3;
-  uint4 cur[4], nxt[4];
+  uint4 cur[CPT], nxt[PF ? CPT : 1];
   int64_t row = blockIdx.x;
   const uint4 zero = make_uint4(0, 0, 0, 0);
   if (row < p.rows) {
     const uint4* xr = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + row * p.ldx);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xr + tid + j * T) : zero;
+    for (int j = 0; j < CPT; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xr + tid + j * T) : zero;
   }
   int parity = 0;
   for (; row < p.rows; row += gridDim.x, parity ^= 1) {
     const int64_t nrow = row + gridDim.x;
-    if (nrow < p.rows) {
+    if (PF && nrow < p.rows) {
       const uint4* xn = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + nrow * p.ldx);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) nxt[j] = (tid + j * T < nchunks) ? __ldg(xn + tid + j * T) : zero;
+      for (int j = 0; j < CPT; ++j) nxt[j] = (tid + j * T < nchunks) ? __ldg(xn + tid + j * T) : zero;
     }
-    float amax = fmaxf(fmaxf(absmax8(cur[0]), absmax8(cur[1])), fmaxf(absmax8(cur[2]), absmax8(cur[3])));
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) amax = fmaxf(amax, absmax8(cur[j]));
     const float a = block_absmax(amax, red[parity], lane, warp, nwarps);
     const float s = scale_from_absmax(a, p.clip, tid == 0 ? p.scales + row : nullptr);
     const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
@@ -201,15 +207,21 @@ quant_rows_kernel(const HadqParams p) {
     uint32_t* qo = reinterpret_cast<uint32_t*>(p.q + row * (int64_t)(p.n >> 1));
     uint4* yo = p.y_out ? reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.y_out) + row * (int64_t)p.n) : nullptr;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < CPT; ++j) {
       const int c = tid + j * T;
       if (c < nchunks) {
         qo[c] = quant8_u4(cur[j], s, rcp, noclamp);
         if (yo) yo[c] = cur[j];
       }
     }
+    if (PF) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) cur[j] = nxt[j];
+      for (int j = 0; j < CPT; ++j) cur[j] = nxt[j];
+    } else if (nrow < p.rows) {
+      const uint4* xn = reinterpret_cast<const uint4*>(reinterpret_cast<const __half*>(p.x) + nrow * p.ldx);
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xn + tid + j * T) : zero;
+    }
   }
 }
 
@@ -674,8 +686,15 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
   const bool base_ok = (elem_size == 2) && forced != 1 && aligned16(x) && (ldx % 8 == 0) && (n % 8 == 0) &&
                        (!y_out || aligned16(y_out)) && (!do_quant || aligned16(q)) && n <= 32768;
   if (base_ok && K == 0 && do_quant && n >= 64) {
+    // small CTAs of eight chunks per thread when every row can be resident at once (one wave), else persistent CTAs
+    // of four chunks per thread that request their next row early
+    const int threads8 = ((n / 8 + 7) / 8 + 31) / 32 * 32;
+    if (rows >= 256 && rows <= (int64_t)num_sms() * 16 && threads8 <= 512 && rows * (int64_t)threads8 <= (int64_t)num_sms() * 1536) {
+      QR_CUDA(launch_kernel(quant_rows_kernel<8, false>, dim3((unsigned)rows), dim3(threads8), 0, st, use_pdl(p.rows), p));
+      return QR_OK;
+    }
     int threads = ((n / 8 + 3) / 4 + 31) / 32 * 32;
-    QR_CUDA(launch_kernel(quant_rows_kernel, dim3(persistent_grid(rows, threads, 1024)), dim3(threads), 0, st,
+    QR_CUDA(launch_kernel(quant_rows_kernel<4, true>, dim3(persistent_grid(rows, threads, 1024)), dim3(threads), 0, st,
                           use_pdl(p.rows), p));
     return QR_OK;
   }
