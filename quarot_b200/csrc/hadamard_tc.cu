@@ -161,6 +161,7 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
     // hadK -> swizzled K-major A tiles (zero padded), zero the k padding rows of the token-row buffers
     const int t = threadIdx.x - 32, nt = kTcThreads - 32;
     const int rows = p.MT * 128, K = p.K;
+    const bool dup_rows = p.MT == 2 && K - 128 <= 64;
     const int chunks = rows * p.KA * 8;                       // 16-byte chunks of the A operand
     const bool vec = (K & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.had_k) & 7) == 0);
     // twelve chunks per thread and round (one round for K <= 172): all loads of a round are issued before its
@@ -182,8 +183,10 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
           const int r = rem >> 3, ch = rem & 7;
           const int c0 = ka * 64 + ch * 8;                      // first hadK column of this chunk
           dst[u] = (uint32_t)(ka * a_atom_bytes + r * 128 + ((ch ^ (r & 7)) << 4));
-          if (r < K && c0 < K) {
-            const __half* src = p.had_k + (size_t)r * K + c0;
+          // second copy of the rows of the second tile, 64 rows further down (see the epilogue)
+          const int hr = (dup_rows && r >= 192) ? r - 64 : r;
+          if (hr < K && c0 < K && (hr == r || hr >= 128)) {
+            const __half* src = p.had_k + (size_t)hr * K + c0;
             if (vec) {      // K % 4 == 0: the chunk starts on an 8-byte boundary and holds 4 or 8 valid columns
               lo[u] = __ldg(reinterpret_cast<const uint2*>(src));
               if (c0 + 8 <= K) hi[u] = __ldg(reinterpret_cast<const uint2*>(src + 4));
@@ -272,9 +275,16 @@ hadq_tc_kernel(const __grid_constant__ CUtensorMap tmX, const HadqTcParams p) {
     const int set = (warp - 2) >> 3;           // set r handles row r of every pair
     const int ew = (warp - 2) & 7;
     const int mt = ew >> 2, q4 = warp & 3;
-    const int kprime = mt * 128 + q4 * 32 + lane;
-    const bool warp_active = (mt * 128 + q4 * 32) < p.K && mt < p.MT;
-    const bool active = kprime < p.K && mt < p.MT;
+    // Scheduler balance: a warp's tensor-memory lanes (and its scheduler) follow from its id modulo 4.  When the second
+    // tile of hadK holds at most 64 rows (172 = 128 + 44), the set-up wrote them twice, at rows 0 .. and 64 .. of the
+    // tile, so that the warps of set 0 read them from lane quarters 0 and 1 and those of set 1 from quarters 2 and 3:
+    // every scheduler then carries three busy epilogue warps per pair of token rows instead of four on two of them
+    // and two on the others.
+    const bool dup_rows = p.MT == 2 && p.K - 128 <= 64;
+    const int q_row = (dup_rows && mt == 1 && set == 1) ? q4 - 2 : q4;      // quarter of the tile's rows this warp finishes
+    const int kprime = mt * 128 + q_row * 32 + lane;
+    const bool warp_active = q_row >= 0 && (mt * 128 + q_row * 32) < p.K && mt < p.MT;
+    const bool active = q_row >= 0 && kprime < p.K && mt < p.MT;
     const int n = p.K * 64;
     uint32_t i = 0;
     for (int64_t pair = blockIdx.x; pair < npairs; pair += gridDim.x, ++i) {
