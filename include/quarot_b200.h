@@ -197,7 +197,7 @@ int qr_quant_linear_i4_f16(const void* x, int64_t ldx, float clip, const uint8_t
  * token rows fit into shared memory (K up to about 54 000 / 26 000 / 12 000 values for up to 8 / 16 / 32 rows).  What is
  * left -- 33 to 64 rows, or longer rows -- runs on a tcgen05 kernel.  There wide layers
  * get there by dealing the weight rows out to the SMs, which needs no scratch.  A narrow layer (at most 48 weight rows
- * per SM, e.g. N = 4096) would leave most of every 128-row MMA idle that way; its (128-row tile, k stage) units are
+ * per SM, e.g. N = 4096) with long rows (K above 8192) would leave most of every 128-row MMA idle that way; its (128-row tile, k stage) units are
  * dealt out instead, a tile may then be shared by several CTAs, and its pieces meet in a caller-provided scratch
  * buffer: int32 partial sums added with integer atomics (exact, order independent) plus one arrival counter per
  * tile; the piece that arrives last finishes the tile, nobody waits.  qr_linear_workspace_bytes returns the bytes

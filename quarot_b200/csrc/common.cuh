@@ -24,7 +24,7 @@ struct Tuning {
   int gemm_pst = 4;           // packed staging slots of the 1-CTA GEMM at BN = 256 (4 or 3)
   int gemm_grid = 0;          // cap on the number of persistent CTAs / clusters (0 = one per SM / SM pair)
   int gemm_decode_max_m = 64; // token rows up to which the weight-streaming kernels are used (decode)
-  int gemm_splitk = 1;        // decode, narrow layers: deal out (tile, stage) units when a workspace is given
+  int gemm_splitk = 1;        // tcgen05 decode kernel, narrow layers: deal out (tile, stage) units through scratch memory: 0 never, 1 for K > 8192 (measured cross-over), 2 always
   int gemm_2sm = 1;           // prefill: 2-CTA kernel (cta_group::2) instead of the 1-CTA kernel
   int gemm_tma_out = 1;       // 2-CTA kernel: tiled TMA stores of the output where alignment allows
   int gemv_max_m = 0;         // token rows up to which the weight-streaming CUDA-core (dp4a) kernel is used (it also serves the quantiser-fused call)

@@ -224,8 +224,10 @@ def tcgen05_decode_kernel():
     decode kernel behind it (33 .. 64 rows, or rows of more values than fit into shared memory), so they switch the
     other one off."""
     _lib.set_tuning("gemv_mma_max_m", 0)
+    _lib.set_tuning("gemm_splitk", 2)          # narrow layers through scratch memory whatever K (default: K > 8192 only)
     yield
     _lib.set_tuning("gemv_mma_max_m", 32)
+    _lib.set_tuning("gemm_splitk", 1)
 
 
 @pytest.mark.usefixtures("tcgen05_decode_kernel")
@@ -303,6 +305,10 @@ def test_workspace_argument_errors():
     assert _lib.lib.qr_linear_workspace_bytes(2, 4096, 4096) == 0
     assert _lib.lib.qr_linear_workspace_bytes(32, 4096, 4096) == 0
     assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 4096) > 0
+    _lib.set_tuning("gemm_splitk", 1)                                     # the default: scratch only for long rows
+    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 4096) == 0
+    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 11008) > 0
+    _lib.set_tuning("gemm_splitk", 2)
     assert _lib.lib.qr_linear_workspace_bytes(32, 4096, 28672) > 0       # rows too long for that kernel's shared memory
 
 
