@@ -27,6 +27,7 @@ struct Tuning {
   int gemm_splitk = 1;        // tcgen05 decode kernel, narrow layers: deal out (tile, stage) units through scratch memory: 0 never, 1 for K > 8192 (measured cross-over), 2 always
   int gemm_2sm = 1;           // prefill: 2-CTA kernel (cta_group::2) instead of the 1-CTA kernel
   int gemm_tma_out = 1;       // 2-CTA kernel: tiled TMA stores of the output where alignment allows
+  int gemm_tail_help = 1;     // 2-CTA kernel: idle warps share the epilogue of a CTA's last tile
   int gemv_max_m = 0;         // token rows up to which the weight-streaming CUDA-core (dp4a) kernel is used (it also serves the quantiser-fused call)
   int gemv_mma_max_m = 32;    // token rows up to which the weight-streaming mma.sync kernel is used (0: never)
   int gemm_decode = 1;        // decode: the weight-streaming tcgen05 kernel (0: tokens on the MMA rows as at prefill)

@@ -55,6 +55,7 @@ struct GemmParams {
   int swiglu;            // 2-CTA kernel, fp16 mode: columns [0,128) / [128,256) of a tile are gate / up channels; out = silu(gate) * up
   int bn;                // 2-CTA kernel: N of the pair tile (a multiple of 16, at most 256); 256 unless fp16 mode with one output
   int n_outs;            // 2-CTA kernel: number of output matrices that receive the result (1, or one per GPU of a column split)
+  int tail_help;         // 2-CTA kernel: warps that have run out of work share the epilogue of the CTA's last tile
   int tma_out;           // 2-CTA kernel: the output has a tensor map (16-byte aligned base and row pitch): tiled stores
   int* status;
 };
@@ -341,7 +342,7 @@ struct SmemLayout2 {
   static constexpr int kScaleOff = kStageOff + kEpiWarps * 4096;     // per epilogue warp: the tile's 256 column scales as fp32
   static constexpr int kBiasOff = kScaleOff + kEpiWarps * 1024;      // per epilogue warp: the tile's 256 bias values (fp16)
   static constexpr int kBarOff = kBiasOff + kEpiWarps * 512;
-  static constexpr int kNumBars = 2 * PST + 2 * IST + 4;
+  static constexpr int kNumBars = 2 * PST + 2 * IST + 4 + 4;      // ..., and one "scales staged" barrier per lane quarter
   static constexpr int kTmemSlotOff = kBarOff + kNumBars * 8;
   static constexpr int kAbortOff = kTmemSlotOff + 8;
   static constexpr int kTotal = kAbortOff + 16;   // abort flag, issuer turn, scratch word
@@ -368,6 +369,48 @@ __device__ __forceinline__ int widen_index2(int w) {
   if (w == 0) return 0;
   if (w < 6 || (w & 3) == 1) return -1;
   return w - 5 - ((w - 5) >> 2);   // 6,7,8 -> 1,2,3; 10,11,12 -> 4,5,6; 14,15,16 -> 7,8,9; 18,19 -> 10,11
+}
+
+// fp16 epilogue of 64 accumulator columns for the warps that help with the last tile of a CTA (see the end of the
+// kernel): the arithmetic and the staging pattern of the epilogue warps' inline code, kept out of line so that it does
+// not add to the register count of the hot loops.
+__device__ __noinline__ void store_block64(uint32_t taddr, const float* sq, const __half* bias, float sp, unsigned char* stg,
+                                           uint32_t stg_u32, int lane, const CUtensorMap* maps, int n_outs, int g0, int x, int y,
+                                           bool in_range) {
+  const uint32_t my_sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+  for (int h = 0; h < 2; ++h) {
+    uint32_t r[32];
+    tmem_ld32(taddr + 32 * h, r);
+    tmem_ld_wait();
+    uint4 pk[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __half2* hh = reinterpret_cast<__half2*>(&pk[e]);
+      const int jc = 32 * h + 8 * e;
+      const float4 s0 = *reinterpret_cast<const float4*>(sq + jc);
+      const float4 s1 = *reinterpret_cast<const float4*>(sq + jc + 4);
+      hh[0] = __floats2half2_rn((float)(int32_t)r[8 * e + 0] * (sp * s0.x), (float)(int32_t)r[8 * e + 1] * (sp * s0.y));
+      hh[1] = __floats2half2_rn((float)(int32_t)r[8 * e + 2] * (sp * s0.z), (float)(int32_t)r[8 * e + 3] * (sp * s0.w));
+      hh[2] = __floats2half2_rn((float)(int32_t)r[8 * e + 4] * (sp * s1.x), (float)(int32_t)r[8 * e + 5] * (sp * s1.y));
+      hh[3] = __floats2half2_rn((float)(int32_t)r[8 * e + 6] * (sp * s1.z), (float)(int32_t)r[8 * e + 7] * (sp * s1.w));
+      if (bias) {
+        const uint4 bb = *reinterpret_cast<const uint4*>(bias + jc);
+        const __half2* bh = reinterpret_cast<const __half2*>(&bb);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) hh[q] = __hadd2(hh[q], bh[q]);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      *reinterpret_cast<uint4*>(stg + lane * 128 + ((((uint32_t)(4 * h + e)) ^ my_sw) << 4)) = pk[e];
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0 && in_range) {
+    for (int i = 0, g = g0 % n_outs; i < n_outs; ++i, g = (g + 1 == n_outs) ? 0 : g + 1) tma_store_2d(&maps[g], stg_u32, x, y);
+    bulk_commit_group();
+  }
 }
 
 // fp16 epilogue of 16 accumulator columns (tile widths that are not a multiple of 64): dequantise, stage as 32 rows x 32
@@ -428,6 +471,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
   auto empty_i = [&](int s) { return bar_base + 8u * (2 * PST + IST + s); };
   auto acc_full = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + a); };
   auto acc_empty = [&](int a) { return bar_base + 8u * (2 * PST + 2 * IST + 2 + a); };
+  auto scales_staged = [&](int q) { return bar_base + 8u * (2 * PST + 2 * IST + 4 + q); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kTmemSlotOff);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::kAbortOff);
   volatile uint32_t* turn = reinterpret_cast<volatile uint32_t*>(smem_gen + L::kAbortOff + 4);   // next k-block to issue
@@ -443,6 +487,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
     for (int s = 0; s < PST; ++s) { mbar_init(full_p(s), 1); mbar_init(empty_p(s), kWidenWarpsPerGroup2); }   // the warps of the owning group
     for (int s = 0; s < IST; ++s) { mbar_init(full_i(s), 2 * kWidenWarpsPerGroup2); mbar_init(empty_i(s), 1); }      // local + remote warps of the group
     for (int a = 0; a < 2; ++a) { mbar_init(acc_full(a), 2); mbar_init(acc_empty(a), 2 * kEpiWarps); }
+    for (int q = 0; q < 4; ++q) mbar_init(scales_staged(q), 1);
     *abort_flag = 0;
     *turn = 0;
     fence_mbar_init();
@@ -586,6 +631,10 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         }
         __syncwarp();
       }
+      // The last tile of this CTA has no main loop behind it to hide its epilogue: the warps that have run out of work
+      // take three quarters of it (end of the kernel); they read the scales this warp has just staged.
+      const bool shared_tile = MODE == MODE_F16 && p.tma_out && !p.swiglu && p.tail_help && tile + num_clusters >= num_tiles;
+      if (shared_tile && lane == 0) mbar_arrive(scales_staged(q4));
       if (!mbar_wait(acc_full(a), pha, abort_flag, p.status, 14)) { ok = false; break; }
       tc_fence_after();
       const int prow = tp * 2 * kBM + (int)rank * kBM + prow_in_tile;
@@ -657,6 +706,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         constexpr int full_cols = (MODE == MODE_I32) ? bn : (bn & ~63);    // fp16: whole 64-column blocks, then 16-column pieces
 #pragma unroll 1
         for (int c0 = 0; c0 < full_cols; c0 += CW) {
+          if (shared_tile && c0 > 0) break;      // the helpers take the other blocks
 #pragma unroll
           for (int h = 0; h < CW / 32; ++h) {
             uint32_t r[32];
@@ -708,7 +758,6 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
           __syncwarp();
           if (lane == 0 && row0 < p.rowsP && tq * bn + c0 < p.rowsQ) {
             // one tiled store per destination: the block goes to this GPU's output and, in a column split, straight
-            // into the peers' copies of the full matrix over NVLink
             // into the peers' copies of the full matrix over NVLink; the destinations are visited in an order that differs
             // from warp to warp and tile to tile, so that the ranks do not all write to the same peer at the same time
             for (int i = 0, g = (int)((tl + warp) % (uint32_t)p.n_outs); i < p.n_outs; ++i, g = (g + 1 == p.n_outs) ? 0 : g + 1)
@@ -716,7 +765,7 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
             bulk_commit_group();
           }
         }
-        if (MODE == MODE_F16 && (bn & 63) != 0) {
+        if (MODE == MODE_F16 && (bn & 63) != 0 && !shared_tile) {
           // tile widths that are not a multiple of 64 (chosen so that the tiles fill whole waves of clusters): the
           // remaining columns leave as 16-column pieces through a second tensor map (32 rows x 32 bytes, unswizzled)
 #pragma unroll 1
@@ -828,6 +877,55 @@ gemm_i4_2sm_kernel(const __grid_constant__ CUtensorMap tmP, const __grid_constan
         if (lane == 0) {
           mbar_arrive_cluster_relaxed(leader_full_i0 + 8u * si);
         }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- the last tile's epilogue, shared
+  // After the last MMA of a CTA only its four epilogue warps would still have work (a quarter of the accumulator each,
+  // four 64-column blocks one after the other) while sixteen warps idle, and nothing hides that time.  Three more
+  // warps per tensor-memory lane quarter (warp id modulo 4: the widen warps on quarters 0, 2, 3; the idle warp, the
+  // producer and one issuer on quarter 1) therefore take the blocks behind the first; their staging blocks lie in the
+  // int8 operand ring, which nothing reads once the accumulator is complete.
+  if (MODE == MODE_F16 && p.tma_out && !p.swiglu && p.tail_help) {
+    __syncwarp();                       // single-thread roles: the rest of the warp has waited here
+    const int q4 = warp & 3;
+    int hr = -1;
+    if (!is_epilogue_warp2(warp)) {
+      if (q4 == 1) hr = warp == 17 ? 0 : warp == kProducerWarp2 ? 1 : warp == kIssuerBWarp ? 2 : -1;
+      else hr = warp == 0 ? 0 : (warp >> 2) - 1;
+      if (hr > 2) hr = -1;
+    }
+    const int my_tiles = cluster_id < num_tiles ? (num_tiles - cluster_id + num_clusters - 1) / num_clusters : 0;
+    if (hr >= 0 && my_tiles > 0 && !*abort_flag) {
+      const uint32_t tl = (uint32_t)(my_tiles - 1);
+      const int tile = cluster_id + (int)tl * num_clusters;
+      const int tp = tile % p.tilesP, tq = tile / p.tilesP;
+      const int a = tl % ACC;
+      const uint32_t pha = (tl / ACC) & 1;
+      pdl_wait();   // the output belongs to the preceding kernels
+      if (mbar_wait(scales_staged(q4), 0, abort_flag, p.status, 18) && mbar_wait(acc_full(a), pha, abort_flag, p.status, 19)) {
+        tc_fence_after();
+        const float* sqf = reinterpret_cast<const float*>(smem_gen + L::kScaleOff + q4 * 1024);
+        const __half* bsh = reinterpret_cast<const __half*>(smem_gen + L::kBiasOff + q4 * 512);
+        const int prow = tp * 2 * kBM + (int)rank * kBM + q4 * 32 + lane;
+        const float sp = prow < p.rowsP ? __half2float(p.sP[prow]) : 0.0f;
+        const int row0 = tp * 2 * kBM + (int)rank * kBM + q4 * 32;
+        unsigned char* stg = smem_gen + L::kI8Off + (q4 * 3 + hr) * 4096;
+        const uint32_t stg_u32 = smem_base + L::kI8Off + (q4 * 3 + hr) * 4096;
+        constexpr int full_cols = bn & ~63;
+        const int c0 = 64 * (hr + 1);
+        const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(a * kBN2);
+        if (c0 < full_cols) {
+          store_block64(taddr + c0, sqf + c0, p.bias ? bsh + c0 : nullptr, sp, stg, stg_u32, lane, &tmOs.m[0], p.n_outs,
+                        (int)tl + warp, tq * bn + c0, row0, row0 < p.rowsP && tq * bn + c0 < p.rowsQ);
+        } else if (c0 == full_cols) {
+#pragma unroll 1
+          for (int c1 = full_cols; c1 < bn; c1 += 16)
+            store_tail_piece(taddr + c1, sqf + c1, p.bias ? bsh + c1 : nullptr, sp, stg, stg_u32, lane, &tmTail, tq * bn + c1, row0,
+                             row0 < p.rowsP && tq * bn + c1 < p.rowsQ);
+        }
+        if (lane == 0) bulk_wait_read_all();   // the staging block must outlive the TMA unit's reads of it
       }
     }
   }
@@ -1015,7 +1113,7 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
   GemmParams p;
   p.K = (int)K; p.out = out; p.ldo = ldo; p.status = status;
   p.bias = reinterpret_cast<const __half*>(bias);
-  p.tma_out = 0; p.n_outs = 1; p.swiglu = 0; p.bn = kBN2;
+  p.tma_out = 0; p.n_outs = 1; p.swiglu = 0; p.bn = kBN2; p.tail_help = g_tuning.gemm_tail_help;
   if (swiglu) {
     if (M <= kBM || g_tuning.gemm_2sm == 0)
       return fail(QR_EUNSUPPORTED, "%s: served by the prefill kernel only (more than %d rows)", who, kBM);
