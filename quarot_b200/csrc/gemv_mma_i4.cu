@@ -24,9 +24,12 @@
 // its range in groups of 16 rows (rows of the last group beyond the range are not loaded and their accumulators are
 // not stored), and its eight warps split the K range of every group eight ways; their partial fragments meet in
 // shared memory behind one barrier per group (two alternating areas), after which all threads add up and store one
-// element each.  Every lane keeps the loads of the next four 64-byte pieces of its two rows in flight while it
-// computes the current four, also across groups.
+// element each.  Every lane holds four (eight for long rows) 64-byte pieces of its two rows in a rotating register
+// buffer: a slot is refilled with the piece that many pieces ahead as soon as its MMAs have been issued, also across
+// groups, so three to four (seven to eight) pieces per row and lane are always in flight.  The token rows come in
+// as one bulk copy per row on the TMA unit.
 #include "common.cuh"
+#include "tc_ptx.cuh"
 
 namespace qr {
 
@@ -40,17 +43,30 @@ struct GemvMmaParams {
   int64_t ldo;
   int M, N, K;
   int a_stride;          // bytes between token rows in shared memory (K / 2 + 64)
+  int* status;           // device status word: a wait that ran out of time leaves its code there
 };
 
 constexpr int kGmWarps = 8;
 constexpr int kGmThreads = 32 * kGmWarps;
-constexpr int kGmUnroll = 4;       // 64-byte pieces per row and loop iteration
+#ifndef GM_U
+#define GM_U 8
+#endif
+#ifndef GM_MINB
+#define GM_MINB 2
+#endif
+constexpr int U = GM_U;    // 64-byte pieces per row that a lane keeps in flight
 
 __device__ __forceinline__ uint4 gm_ld_stream16(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
+}
+
+// Untiled bulk copy global -> shared memory on the TMA unit; both addresses 16-byte aligned, the size a multiple of 16.
+__device__ __forceinline__ void gm_bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -60,18 +76,27 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t 
 }
 
 // NF: fragments of eight token rows (1: M <= 8, 2: M <= 16, 4: M <= 32)
-template <int NF, bool F16>
+// U: 64-byte pieces per row that a lane keeps in flight (4, or 8 where a warp's slice of K is a multiple of eight pieces)
+template <int NF, bool F16, int U>
 __global__ void __launch_bounds__(kGmThreads, 2)
 gemv_mma_i4_kernel(const GemvMmaParams p) {
   constexpr int MT = 8 * NF;
   constexpr int kFrag = NF * 4 * 32;                           // ints of one warp's accumulator fragments
   extern __shared__ __align__(16) unsigned char gm_smem[];     // MT padded token rows, then two reduction areas
   __shared__ float s_scale[MT];
+  __shared__ __align__(8) uint64_t s_rows_bar;                 // completes when the token rows have landed
+  __shared__ int s_abort;
   const int kbytes = p.K >> 1;
   const int nchunks = kbytes >> 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
   pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
+  const uint32_t rows_bar = smem_u32(&s_rows_bar);
+  if (threadIdx.x == 0) {
+    mbar_init(rows_bar, 1);
+    s_abort = 0;
+    fence_mbar_init();
+  }
 
   // this CTA's rows, this warp's slice of K (a multiple of the four chunks a warp takes per row and step)
   const int row_begin = (int)((long long)blockIdx.x * p.N / gridDim.x);
@@ -80,34 +105,40 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
   const int c_begin = warp * cps;
   const int c_end = (c_begin + cps < nchunks) ? c_begin + cps : nchunks;
   const int steps = c_begin < c_end ? (c_end - c_begin + 3) >> 2 : 0;
-  const int iters = (steps + kGmUnroll - 1) / kGmUnroll;
+  const int iters = (steps + U - 1) / U;
 
-  auto load_iter = [&](int rb, int it, uint4 (&w)[kGmUnroll][2]) {
+  // piece u of iteration it of the group of rows at rb: 16 bytes of rows rb + g and rb + g + 8
+  auto load_piece = [&](int rb, int it, int u, uint4 (&w)[2]) {
     const int r0 = rb + g, r1 = r0 + 8;
-    const uint8_t* p0 = p.B + (size_t)r0 * kbytes;
-    const uint8_t* p1 = p.B + (size_t)r1 * kbytes;
-#pragma unroll
-    for (int u = 0; u < kGmUnroll; ++u) {
-      const int c = c_begin + ((it * kGmUnroll + u) << 2) + t;
-      const bool ok = c < c_end;
-      w[u][0] = (ok && r0 < row_end) ? gm_ld_stream16(p0 + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
-      w[u][1] = (ok && r1 < row_end) ? gm_ld_stream16(p1 + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
-    }
+    const int c = c_begin + ((it * U + u) << 2) + t;
+    const bool ok = c < c_end;
+    w[0] = (ok && r0 < row_end) ? gm_ld_stream16(p.B + (size_t)r0 * kbytes + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+    w[1] = (ok && r1 < row_end) ? gm_ld_stream16(p.B + (size_t)r1 * kbytes + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
   };
 
-  uint4 cur[kGmUnroll][2], nxt[kGmUnroll][2];
-  // The weights do not depend on the kernel in front: the first chunks are requested before the programmatic-
+  uint4 cur[U][2];
+  // The weights do not depend on the kernel in front: the first pieces are requested before the programmatic-
   // dependency wait and before the token rows are staged.
-  if (row_begin < row_end && iters > 0) load_iter(row_begin, 0, cur);
+  if (row_begin < row_end && iters > 0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) load_piece(row_begin, 0, u, cur[u]);
+  }
   pdl_wait();   // token rows, scales and the output belong to the preceding kernels
-  for (int i = threadIdx.x; i < MT * nchunks; i += kGmThreads) {
-    const int m = i / nchunks, c = i - m * nchunks;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (m < p.M) v = *reinterpret_cast<const uint4*>(p.A + (size_t)m * kbytes + (size_t)c * 16);
-    *reinterpret_cast<uint4*>(gm_smem + (size_t)m * p.a_stride + (size_t)c * 16) = v;
+  // The token rows come in as one bulk copy each (the TMA unit moves them while the warps wait for nothing else:
+  // a loop of loads and stores would pay one trip to the L2 per few chunks); rows beyond M are zero.
+  if (threadIdx.x == 0) {
+    mbar_expect_tx(rows_bar, (uint32_t)p.M * (uint32_t)kbytes);
+    for (int m = 0; m < p.M; ++m)
+      gm_bulk_load(smem_u32(gm_smem + (size_t)m * p.a_stride), p.A + (size_t)m * kbytes, (uint32_t)kbytes, rows_bar);
+  }
+  for (int i = threadIdx.x; i < (MT - p.M) * nchunks; i += kGmThreads) {
+    const int m = p.M + i / nchunks, c = i % nchunks;
+    *reinterpret_cast<uint4*>(gm_smem + (size_t)m * p.a_stride + (size_t)c * 16) = make_uint4(0, 0, 0, 0);
   }
   if (F16 && threadIdx.x < MT) s_scale[threadIdx.x] = threadIdx.x < p.M ? __half2float(p.sA[threadIdx.x]) : 0.0f;
   __syncthreads();
+  // bounded wait; if it runs out of time the status word says so and the whole CTA leaves (nothing else is in flight)
+  if (!__syncthreads_and(mbar_wait(rows_bar, 0, &s_abort, p.status, 61) ? 1 : 0)) return;
   int* red = reinterpret_cast<int*>(gm_smem + (size_t)MT * p.a_stride);       // [2][warp][kFrag]
 
   int parity = 0;
@@ -133,21 +164,18 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
     }
 #pragma unroll 1
     for (int it = 0; it < iters; ++it) {
-      // the next iteration's chunks (of this group, or the first of the next group) are requested before this
-      // iteration is computed
-      if (it + 1 < iters) load_iter(rb, it + 1, nxt);
-      else if (rb + 16 < row_end) load_iter(rb + 16, 0, nxt);
+      const bool more = it + 1 < iters, next_group = rb + 16 < row_end;
 #pragma unroll
-      for (int u = 0; u < kGmUnroll; ++u) {
-        const int c = c_begin + ((it * kGmUnroll + u) << 2) + t;
-        const uint32_t w0[4] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w};
-        const uint32_t w1[4] = {cur[u][1].x, cur[u][1].y, cur[u][1].z, cur[u][1].w};
+      for (int u = 0; u < U; ++u) {
+        const int c = c_begin + ((it * U + u) << 2) + t;
         // chunks at or beyond c_end meet zero weights; the address stays inside the padded token row
         const int cc = c < nchunks ? c : 0;
         uint4 xa[NF];
 #pragma unroll
         for (int f = 0; f < NF; ++f)
           xa[f] = *reinterpret_cast<const uint4*>(gm_smem + (size_t)(8 * f + g) * p.a_stride + (size_t)cc * 16);
+        const uint32_t w0[4] = {cur[u][0].x, cur[u][0].y, cur[u][0].z, cur[u][0].w};
+        const uint32_t w1[4] = {cur[u][1].x, cur[u][1].y, cur[u][1].z, cur[u][1].w};
         // word j of the chunks feeds MMA j of every fragment; consecutive MMAs go to different accumulators
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -159,11 +187,15 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
             mma_s8_16832(acc[f], a0, a1, a2, a3, (xw << 4) & 0xF0F0F0F0u, xw & 0xF0F0F0F0u);
           }
         }
+        // the slot is free again: it takes the piece that is U pieces ahead (of this group, or the first of the next
+        // group), so every lane always has U - 1 or U pieces of its two rows in flight
+        if (more) load_piece(rb, it + 1, u, cur[u]);
+        else if (next_group) load_piece(rb + 16, 0, u, cur[u]);
       }
-#pragma unroll
-      for (int u = 0; u < kGmUnroll; ++u) { cur[u][0] = nxt[u][0]; cur[u][1] = nxt[u][1]; }
     }
     // the eight partial fragments meet in shared memory; the areas alternate, so one barrier per group is enough
+    // (taking the sums one group later behind mbarriers instead was measured slower: 7.3 against 6.95 us for the 7B
+    // qkv layer)
     int* area = red + parity * (kGmWarps * kFrag);
 #pragma unroll
     for (int f = 0; f < NF; ++f)
@@ -207,12 +239,12 @@ bool gemv_mma_serves(int64_t M, int64_t K) {
   return gemv_mma_smem(M <= 8 ? 1 : (M <= 16 ? 2 : 4), K) <= kGmSmemMax;
 }
 
-template <int NF, bool F16>
-static int launch_gemv_mma_nf(GemvMmaParams& p, cudaStream_t st) {
+template <int NF, bool F16, int U>
+static int launch_gemv_mma_u(GemvMmaParams& p, cudaStream_t st) {
   p.a_stride = (p.K >> 1) + 64;
   const size_t smem = gemv_mma_smem(NF, p.K);
   if (smem > kGmSmemMax) return QR_EUNSUPPORTED;
-  auto kern = gemv_mma_i4_kernel<NF, F16>;
+  auto kern = gemv_mma_i4_kernel<NF, F16, U>;
   static thread_local size_t configured[64] = {0};
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
@@ -229,6 +261,17 @@ static int launch_gemv_mma_nf(GemvMmaParams& p, cudaStream_t st) {
   return QR_OK;
 }
 
+// A lane keeps eight pieces per row in flight where a warp's slice of K is a whole number of such iterations (long
+// rows: K = 8192, 16384, ...; 70B gate/up with eight token rows 45.6 -> 42.4 us), else four (K = 4096: one iteration
+// per group of rows; eight would idle through four pieces of zeros).
+template <int NF, bool F16>
+static int launch_gemv_mma_nf(GemvMmaParams& p, cudaStream_t st) {
+  const int nchunks = p.K >> 5;
+  const int pieces = ((((nchunks + kGmWarps - 1) / kGmWarps) + 3) & ~3) >> 2;
+  if (pieces % 8 == 0) return launch_gemv_mma_u<NF, F16, 8>(p, st);
+  return launch_gemv_mma_u<NF, F16, 4>(p, st);
+}
+
 // Returns QR_EUNSUPPORTED when the shape is not one this kernel serves (the caller then takes another path).
 int launch_gemv_mma_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
                        const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st) {
@@ -238,6 +281,8 @@ int launch_gemv_mma_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N,
   p.A = A; p.B = B; p.sA = reinterpret_cast<const __half*>(sA); p.sB = reinterpret_cast<const __half*>(sB);
   p.bias = reinterpret_cast<const __half*>(bias); p.out = out; p.ldo = ldo;
   p.M = (int)M; p.N = (int)N; p.K = (int)K; p.a_stride = 0;
+  p.status = kernel_status_ptr();
+  if (!p.status) return QR_ENOTREADY;
   if (f16) {
     if (M <= 8) return launch_gemv_mma_nf<1, true>(p, st);
     if (M <= 16) return launch_gemv_mma_nf<2, true>(p, st);
