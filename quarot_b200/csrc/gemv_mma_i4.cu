@@ -19,7 +19,8 @@
 // serve token rows 8 .. 15 and 16 .. 31.  The accumulators are 256 x the dot products, as everywhere else, and the epilogue is
 // the arithmetic of the other forms of kernel (b): bit-identical results.
 //
-// Parallelism and balance.  One or two persistent CTAs of eight warps per SM; the weight rows are dealt out to the
+// Parallelism and balance.  Two persistent CTAs of eight warps per SM, or one of sixteen (two halves that take
+// alternate groups of rows and share only the token rows); the weight rows are dealt out to the
 // CTAs as contiguous ranges of N / CTAs rows (any number: every SM streams the same number of bytes), a CTA walks
 // its range in groups of 16 rows (rows of the last group beyond the range are not loaded and their accumulators are
 // not stored), and its eight warps split the K range of every group eight ways; their partial fragments meet in
@@ -43,6 +44,8 @@ struct GemvMmaParams {
   int64_t ldo;
   int M, N, K;
   int a_stride;          // bytes between token rows in shared memory (K / 2 + 64)
+  int red_areas;         // reduction areas per half of the CTA: 2 (alternating, one barrier per group), or 1 where
+                         // shared memory is short (a second barrier per group protects the area)
   int* status;           // device status word: a wait that ran out of time leaves its code there
 };
 
@@ -77,8 +80,11 @@ __device__ __forceinline__ void mma_s8_16832(int (&c)[4], uint32_t a0, uint32_t 
 
 // NF: fragments of eight token rows (1: M <= 8, 2: M <= 16, 4: M <= 32)
 // U: 64-byte pieces per row that a lane keeps in flight (4, or 8 where a warp's slice of K is a multiple of eight pieces)
-template <int NF, bool F16, int U>
-__global__ void __launch_bounds__(kGmThreads, 2)
+// H: halves of a CTA.  Where the token rows leave room for one CTA per SM only, that CTA has sixteen warps: two halves
+//    of eight that take alternate groups of rows and share nothing but the token rows (own reduction areas, own
+//    named barrier), so the SM keeps as many warps and as many loads in flight as with two CTAs.
+template <int NF, bool F16, int U, int H>
+__global__ void __launch_bounds__(kGmThreads * H, 2 / H)
 gemv_mma_i4_kernel(const GemvMmaParams p) {
   constexpr int MT = 8 * NF;
   constexpr int kFrag = NF * 4 * 32;                           // ints of one warp's accumulator fragments
@@ -88,7 +94,9 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
   __shared__ int s_abort;
   const int kbytes = p.K >> 1;
   const int nchunks = kbytes >> 4;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = (threadIdx.x >> 5) & (kGmWarps - 1), lane = threadIdx.x & 31;    // warp: index within the half
+  const int half = H > 1 ? (int)(threadIdx.x / kGmThreads) : 0;
+  const int htid = threadIdx.x & (kGmThreads - 1);
   const int g = lane >> 2, t = lane & 3;
   pdl_launch_dependents();   // the next kernel of the stream may be brought up; it waits for this grid to finish
   const uint32_t rows_bar = smem_u32(&s_rows_bar);
@@ -119,9 +127,10 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
   uint4 cur[U][2];
   // The weights do not depend on the kernel in front: the first pieces are requested before the programmatic-
   // dependency wait and before the token rows are staged.
-  if (row_begin < row_end && iters > 0) {
+  const int first_rb = row_begin + 16 * half;
+  if (first_rb < row_end && iters > 0) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) load_piece(row_begin, 0, u, cur[u]);
+    for (int u = 0; u < U; ++u) load_piece(first_rb, 0, u, cur[u]);
   }
   pdl_wait();   // token rows, scales and the output belong to the preceding kernels
   // The token rows come in as one bulk copy each (the TMA unit moves them while the warps wait for nothing else:
@@ -131,7 +140,7 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
     for (int m = 0; m < p.M; ++m)
       gm_bulk_load(smem_u32(gm_smem + (size_t)m * p.a_stride), p.A + (size_t)m * kbytes, (uint32_t)kbytes, rows_bar);
   }
-  for (int i = threadIdx.x; i < (MT - p.M) * nchunks; i += kGmThreads) {
+  for (int i = threadIdx.x; i < (MT - p.M) * nchunks; i += kGmThreads * H) {
     const int m = p.M + i / nchunks, c = i % nchunks;
     *reinterpret_cast<uint4*>(gm_smem + (size_t)m * p.a_stride + (size_t)c * 16) = make_uint4(0, 0, 0, 0);
   }
@@ -139,10 +148,14 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
   __syncthreads();
   // bounded wait; if it runs out of time the status word says so and the whole CTA leaves (nothing else is in flight)
   if (!__syncthreads_and(mbar_wait(rows_bar, 0, &s_abort, p.status, 61) ? 1 : 0)) return;
-  int* red = reinterpret_cast<int*>(gm_smem + (size_t)MT * p.a_stride);       // [2][warp][kFrag]
+  int* red = reinterpret_cast<int*>(gm_smem + (size_t)MT * p.a_stride) + half * (p.red_areas * kGmWarps * kFrag);   // [half][area][warp][kFrag]
+  auto half_barrier = [&]() {
+    if (H > 1) asm volatile("bar.sync %0, %1;" ::"r"(1 + half), "r"(kGmThreads) : "memory");   // this half only
+    else __syncthreads();
+  };
 
   int parity = 0;
-  for (int rb = row_begin; rb < row_end; rb += 16, parity ^= 1) {
+  for (int rb = first_rb; rb < row_end; rb += 16 * H, parity ^= (p.red_areas - 1)) {
     int acc[NF][4];
 #pragma unroll
     for (int f = 0; f < NF; ++f)
@@ -155,7 +168,7 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
     if (F16) {
 #pragma unroll
       for (int q = 0; q < kFin; ++q) {
-        const int i = threadIdx.x + q * kGmThreads;
+        const int i = htid + q * kGmThreads;
         const int n = rb + ((i & 31) >> 2) + ((((i >> 5) & 3) >> 1) << 3);
         const bool live = i < kFrag && n < row_end;
         fin_scale[q] = live ? __half2float(__ldg(p.sB + n)) : 0.0f;
@@ -164,7 +177,7 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
     }
 #pragma unroll 1
     for (int it = 0; it < iters; ++it) {
-      const bool more = it + 1 < iters, next_group = rb + 16 < row_end;
+      const bool more = it + 1 < iters, next_group = rb + 16 * H < row_end;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
         const int c = c_begin + ((it * U + u) << 2) + t;
@@ -190,7 +203,7 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
         // the slot is free again: it takes the piece that is U pieces ahead (of this group, or the first of the next
         // group), so every lane always has U - 1 or U pieces of its two rows in flight
         if (more) load_piece(rb, it + 1, u, cur[u]);
-        else if (next_group) load_piece(rb + 16, 0, u, cur[u]);
+        else if (next_group) load_piece(rb + 16 * H, 0, u, cur[u]);
       }
     }
     // the eight partial fragments meet in shared memory; the areas alternate, so one barrier per group is enough
@@ -201,11 +214,11 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
     for (int f = 0; f < NF; ++f)
 #pragma unroll
       for (int e = 0; e < 4; ++e) area[warp * kFrag + (f * 4 + e) * 32 + lane] = acc[f][e];
-    __syncthreads();
+    half_barrier();
     // thread i finishes element i: fragment f, register e, lane l -> channel rb + l / 4 + 8 (e / 2), token 8 f + 2 (l % 4) + e % 2
 #pragma unroll
     for (int q = 0; q < kFin; ++q) {
-      const int i = threadIdx.x + q * kGmThreads;
+      const int i = htid + q * kGmThreads;
       if (i >= kFrag) break;
       int v = 0;
 #pragma unroll
@@ -224,27 +237,42 @@ gemv_mma_i4_kernel(const GemvMmaParams p) {
         }
       }
     }
+    if (p.red_areas == 1) half_barrier();   // the only area is rewritten by the next group
   }
 }
 
-// Shared memory of a CTA: the padded token rows and two reduction areas.
-static size_t gemv_mma_smem(int nf, int64_t K) {
-  return (size_t)(8 * nf) * (size_t)((K >> 1) + 64) + (size_t)2 * kGmWarps * nf * 4 * 32 * sizeof(int);
-}
 constexpr size_t kGmSmemMax = 220 * 1024;
 
+// Shared memory of a CTA: the padded token rows and the reduction areas.
+static size_t gemv_mma_smem(int nf, int64_t K, int halves, int areas) {
+  return (size_t)(8 * nf) * (size_t)((K >> 1) + 64) + (size_t)halves * areas * kGmWarps * nf * 4 * 32 * sizeof(int);
+}
+// Two CTAs of eight warps per SM where their token rows fit, else one CTA of sixteen.
+static bool gemv_mma_two_ctas_fit(int nf, int64_t K) { return 2 * (gemv_mma_smem(nf, K, 1, 2) + 1024) <= 226 * 1024; }
+// One CTA of sixteen warps also where two of eight would fit, if it was measured faster: it halves the copies of the
+// token rows that the SMs pull from the L2 (32 rows of K = 4096, N = 12288: 12.2 -> 10.9 us; 16 rows of K = 11008,
+// N = 4096: 9.6 -> 7.7 us; slower for up to eight rows and for 16 rows of K = 4096).
+static int gemv_mma_halves(int nf, int64_t K) {
+  if (g_tuning.gemv_mma_halves == 2) return 2;
+  if (!gemv_mma_two_ctas_fit(nf, K)) return 2;
+  if (g_tuning.gemv_mma_halves == 1) return 1;
+  return (nf == 4 || (nf == 2 && K >= 8192)) ? 2 : 1;
+}
+static int gemv_mma_areas(int nf, int64_t K, int halves) { return gemv_mma_smem(nf, K, halves, 2) <= kGmSmemMax ? 2 : 1; }
 // Does this kernel take M token rows of K values?  (The token rows have to fit into shared memory.)
 bool gemv_mma_serves(int64_t M, int64_t K) {
   if (M < 1 || M > 32 || K < 32 || K % 32 != 0 || K > 65536) return false;
-  return gemv_mma_smem(M <= 8 ? 1 : (M <= 16 ? 2 : 4), K) <= kGmSmemMax;
+  const int nf = M <= 8 ? 1 : (M <= 16 ? 2 : 4);
+  return gemv_mma_smem(nf, K, gemv_mma_halves(nf, K), 1) <= kGmSmemMax;
 }
 
-template <int NF, bool F16, int U>
-static int launch_gemv_mma_u(GemvMmaParams& p, cudaStream_t st) {
+template <int NF, bool F16, int U, int H>
+static int launch_gemv_mma_h(GemvMmaParams& p, cudaStream_t st) {
   p.a_stride = (p.K >> 1) + 64;
-  const size_t smem = gemv_mma_smem(NF, p.K);
+  p.red_areas = gemv_mma_areas(NF, p.K, H);
+  const size_t smem = gemv_mma_smem(NF, p.K, H, p.red_areas);
   if (smem > kGmSmemMax) return QR_EUNSUPPORTED;
-  auto kern = gemv_mma_i4_kernel<NF, F16, U>;
+  auto kern = gemv_mma_i4_kernel<NF, F16, U, H>;
   static thread_local size_t configured[64] = {0};
   int dev = 0;
   QR_CUDA(cudaGetDevice(&dev));
@@ -252,13 +280,18 @@ static int launch_gemv_mma_u(GemvMmaParams& p, cudaStream_t st) {
     QR_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     if (dev < 64) configured[dev] = smem;
   }
-  const int per_sm = (2 * (smem + 1024) <= 226 * 1024) ? 2 : 1;
-  int64_t grid = (int64_t)num_sms() * per_sm;
+  int64_t grid = (int64_t)num_sms() * (2 / H);
   // every CTA gets N / grid rows, so all SMs stream the same number of bytes; only very small N shrinks the grid
-  const int64_t need = ((int64_t)p.N + 7) / 8;
+  const int64_t need = ((int64_t)p.N + 8 * H - 1) / (8 * H);
   if (grid > need) grid = need;
-  QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGmThreads), smem, st, use_pdl(p.M), p));
+  QR_CUDA(launch_kernel(kern, dim3((unsigned)grid), dim3(kGmThreads * H), smem, st, use_pdl(p.M), p));
   return QR_OK;
+}
+
+template <int NF, bool F16, int U>
+static int launch_gemv_mma_u(GemvMmaParams& p, cudaStream_t st) {
+  if (gemv_mma_halves(NF, p.K) == 2) return launch_gemv_mma_h<NF, F16, U, 2>(p, st);
+  return launch_gemv_mma_h<NF, F16, U, 1>(p, st);
 }
 
 // A lane keeps eight pieces per row in flight where a warp's slice of K is a whole number of such iterations (long
@@ -280,7 +313,7 @@ int launch_gemv_mma_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N,
   GemvMmaParams p;
   p.A = A; p.B = B; p.sA = reinterpret_cast<const __half*>(sA); p.sB = reinterpret_cast<const __half*>(sB);
   p.bias = reinterpret_cast<const __half*>(bias); p.out = out; p.ldo = ldo;
-  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.a_stride = 0;
+  p.M = (int)M; p.N = (int)N; p.K = (int)K; p.a_stride = 0; p.red_areas = 2;
   p.status = kernel_status_ptr();
   if (!p.status) return QR_ENOTREADY;
   if (f16) {
