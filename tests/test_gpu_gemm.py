@@ -421,14 +421,19 @@ def test_quantizer_inside_the_weight_streaming_kernel(M, N, K, clip):
 
 
 
+@pytest.mark.parametrize("halves", [0, 1, 2])
 @pytest.mark.parametrize("M,N,K", [(1, 4096, 4096), (5, 12288, 4096), (8, 4096, 11008), (16, 22016, 4096), (13, 1000, 2048),
                                    (9, 33, 1024), (16, 7, 4096), (12, 300, 1088), (7, 4096, 64), (16, 130, 320),
-                                   (11, 5000, 1152), (16, 17, 192), (2, 64, 20480)])
-def test_weight_streaming_kernel_with_warp_level_mmas(M, N, K):
-    """5 .. 16 token rows (here also fewer, with the CUDA-core kernel switched off): weights straight from global
-    memory into the A fragments of mma.sync.m16n8k32.s8, K split over the warps of a CTA on narrow layers.  Exact
-    int32 accumulators, the epilogue arithmetic of the other kernels, ragged N and K, an output pitch that is not a
-    multiple of anything, repeated launches, with and without programmatic dependent launch."""
+                                   (11, 5000, 1152), (16, 17, 192), (2, 64, 20480),
+                                   (32, 4096, 4096), (24, 1000, 11008), (32, 33, 1024), (17, 300, 1088), (16, 520, 8192),
+                                   (8, 1000, 8192), (32, 260, 8192), (3, 77, 16384), (29, 2500, 4096)])
+def test_weight_streaming_kernel_with_warp_level_mmas(M, N, K, halves):
+    """1 .. 32 token rows: weights straight from global memory into the A fragments of mma.sync.m16n8k32.s8, K split
+    over the warps of a CTA.  Exact int32 accumulators, the epilogue arithmetic of the other kernels, ragged N and K,
+    an output pitch that is not a multiple of anything, repeated launches, with and without programmatic dependent
+    launch; four and eight pieces per row in flight (K = 8192, 16384 take eight); two CTAs of eight warps per SM, one
+    of sixteen (forced, and where the token rows leave no choice: 24 rows of K = 11008 run with a single reduction
+    area per half)."""
     g = torch.Generator().manual_seed(M * 41 + N)
     a, w = _rand_packed(M, K, 91), _rand_packed(N, K, 92)
     sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
@@ -438,6 +443,7 @@ def test_weight_streaming_kernel_with_warp_level_mmas(M, N, K):
     ref = O.sym_dequant_fp32(acc, sx, sw).half()
     ad, wd = a.to(DEV), w.to(DEV)
     _lib.set_tuning("gemv_max_m", 0)
+    _lib.set_tuning("gemv_mma_halves", halves)
     try:
         for pdl in (0, 1):
             _lib.set_tuning("pdl", pdl)
@@ -455,6 +461,7 @@ def test_weight_streaming_kernel_with_warp_level_mmas(M, N, K):
     finally:
         _lib.set_tuning("gemv_max_m", 0)
         _lib.set_tuning("gemv_mma_max_m", 32)
+        _lib.set_tuning("gemv_mma_halves", 0)
         _lib.set_tuning("pdl", 2)
     assert _lib.kernel_status() == 0
 
