@@ -371,16 +371,16 @@ hadq_fast_kernel(const HadqParams p) {
 
     if (KT > 0) {
       // ---- stage 0: raw row -> padded staging, zero the padding rows
-      const int vec_per_k = m >> 3;
+      const int vec_per_k = m >> 3, vshift = p.wbits - 3;     // m is a power of two
       for (int c = tid; c < (n >> 3); c += nthreads) {
-        const int k = c / vec_per_k;
-        const int mm = (c - k * vec_per_k) << 3;
+        const int k = c >> vshift;
+        const int mm = (c & (vec_per_k - 1)) << 3;
         *reinterpret_cast<uint4*>(raw + k * pitch + mm) = __ldg(reinterpret_cast<const uint4*>(xr) + c);
       }
       const int pad_vecs = (KT * 16 - K) * vec_per_k;
       for (int c = tid; c < pad_vecs; c += nthreads) {
-        const int k = K + c / vec_per_k;
-        const int mm = (c % vec_per_k) << 3;
+        const int k = K + (c >> vshift);
+        const int mm = (c & (vec_per_k - 1)) << 3;
         *reinterpret_cast<uint4*>(raw + k * pitch + mm) = make_uint4(0, 0, 0, 0);
       }
       __syncthreads();
@@ -726,6 +726,12 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
     const size_t smem = (size_t)p.n * 4 + raw + 256;
     int threads = (p.n / 32 + 31) / 32 * 32;
     if (KT > 0 && threads < KT * 32) threads = KT * 32;
+    // the dense factor is dealt out as (16-row tile, 64-column chunk) units, one per warp and round: enough warps for
+    // one round where the CTA may be that large (28 x 1024: 32 warps for 2 x 16 units instead of 28)
+    if (KT > 0) {
+      const int one_round = KT * (p.m >> 6) * 32;
+      if (one_round > threads && one_round <= hadq_max_threads(KT)) threads = one_round;
+    }
     if (smem <= 227 * 1024 && threads <= hadq_max_threads(KT)) {
       switch (KT) {
         case 0: return launch_fast<0>(p, threads, smem, st);
