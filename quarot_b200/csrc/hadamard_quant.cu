@@ -129,6 +129,11 @@ __device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4],
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
@@ -364,25 +369,31 @@ hadq_fast_kernel(const HadqParams p) {
   // the table does not depend on the kernel in front, the activations do: its fragments were requested above
   pdl_wait();
 
+  // Kronecker form: the raw row goes to the staging buffer with asynchronous 16-byte copies, so that the next row is
+  // on its way from memory while the current one runs through its passes (the staging buffer is free as soon as the
+  // dense factor has been applied).  The k padding rows of the buffer are zero once and for all.
+  auto stage_row = [&](int64_t r) {
+    const __half* xs = reinterpret_cast<const __half*>(p.x) + r * p.ldx;
+    const int vec_per_k = m >> 3, vshift = p.wbits - 3;     // m is a power of two
+    for (int c = tid; c < (n >> 3); c += nthreads)
+      cp_async16(smem_u32(raw + (c >> vshift) * pitch + ((c & (vec_per_k - 1)) << 3)), xs + (size_t)c * 8);
+  };
+  if (KT > 0) {
+    const int vec_per_k = m >> 3, vshift = p.wbits - 3;
+    const int pad_vecs = (KT * 16 - K) * vec_per_k;
+    for (int c = tid; c < pad_vecs; c += nthreads)
+      *reinterpret_cast<uint4*>(raw + (K + (c >> vshift)) * pitch + ((c & (vec_per_k - 1)) << 3)) = make_uint4(0, 0, 0, 0);
+    if ((int64_t)blockIdx.x < p.rows) stage_row(blockIdx.x);
+  }
+
   int parity = 0;
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
     const __half* xr = reinterpret_cast<const __half*>(p.x) + row * p.ldx;
     int scalar_bits = p.wbits - 5;   // index bits left for the shared-memory passes
 
     if (KT > 0) {
-      // ---- stage 0: raw row -> padded staging, zero the padding rows
-      const int vec_per_k = m >> 3, vshift = p.wbits - 3;     // m is a power of two
-      for (int c = tid; c < (n >> 3); c += nthreads) {
-        const int k = c >> vshift;
-        const int mm = (c & (vec_per_k - 1)) << 3;
-        *reinterpret_cast<uint4*>(raw + k * pitch + mm) = __ldg(reinterpret_cast<const uint4*>(xr) + c);
-      }
-      const int pad_vecs = (KT * 16 - K) * vec_per_k;
-      for (int c = tid; c < pad_vecs; c += nthreads) {
-        const int k = K + (c >> vshift);
-        const int mm = (c & (vec_per_k - 1)) << 3;
-        *reinterpret_cast<uint4*>(raw + k * pitch + mm) = make_uint4(0, 0, 0, 0);
-      }
+      // ---- stage 0: the raw row is in flight to the padded staging buffer (requested one row ahead, see below)
+      cp_async_wait_all();
       __syncthreads();
       // ---- stage 1: D = hadK . X on tensor cores, 64 columns per unit
       const int nchunks = m >> 6;
@@ -457,6 +468,7 @@ hadq_fast_kernel(const HadqParams p) {
       int r1 = scalar_bits <= 5 ? scalar_bits : (scalar_bits + 1) / 2;
       if (r1 > 4 && scalar_bits > 5) r1 = 4;
       __syncthreads();
+      if (KT > 0 && row + gridDim.x < p.rows) stage_row(row + gridDim.x);   // every warp is done with the staging buffer
       switch (r1) {
         case 1: pass_b5<1>(buf32, n, tid, nthreads); break;
         case 2: pass_b5<2>(buf32, n, tid, nthreads); break;
