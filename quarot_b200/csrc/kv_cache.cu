@@ -13,8 +13,10 @@
 //
 // kv_decode_kernel: one CTA per (sequence, head), eight warps taking chunks of 32 cached tokens.  Scores: lane =
 // token, the 64-byte key row against the query in shared memory, dequantisation folded into the dot product
-// (scale * <q, codes> - zero * sum(q)).  Online softmax per warp in base 2.  Values: lane = four head dimensions,
-// one broadcast of p * scale per token, the zero points summed separately.  The eight partial states are merged
+// (scale * <q, codes> - zero * sum(q)).  Online softmax per warp in base 2.  Values: the lane that scored a token
+// also brings its 64-byte value row in (16-byte loads, requested with the key) and parks it in shared memory;
+// then lane = four head dimensions, two bytes and one broadcast of p * scale per token, the zero points summed
+// separately.  The eight partial states are merged
 // through shared memory.  The query's Hadamard transform, which upstream applies with a separate kernel, runs at
 // the start of the same kernel.
 #include "common.cuh"
@@ -166,11 +168,14 @@ __device__ __forceinline__ float kv_peer_float(const float* local, uint32_t rank
   return v;
 }
 
-// Byte `k` (0 .. 3) of `bytes`, a value below 256, as a float without an integer-to-float conversion (those issue at a
-// quarter of the rate of ordinary arithmetic): 0x4B0000vv is 2^23 + vv exactly.
+// Codes as floats without a conversion instruction (those issue at a quarter of the rate of ordinary arithmetic) and
+// without a subtraction: a code c moved to bits 3 .. 6 of a byte, with that byte permuted into bits 16 .. 23 of
+// 0x41000000, is the float 8 + c / 2 exactly.  Sums of w * (8 + c / 2) are turned back into sums of w * c once per
+// row (2 * sum - 16 * sum of w); the bias is of the size of the data, so fp32 loses a bit or two, not the result.
+// `bytes` holds four codes, each already shifted to bits 3 .. 6 of its byte; k selects the byte.
 template <int k>
-__device__ __forceinline__ float byte_to_float(uint32_t bytes) {
-  return __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7440 + k)) - 8388608.0f;
+__device__ __forceinline__ float code_to_biased_float(uint32_t bytes) {
+  return __uint_as_float(__byte_perm(bytes, 0x41000000u, 0x7044 + (k << 8)));
 }
 
 __global__ void __launch_bounds__(32 * kKvDecWarps)
@@ -180,6 +185,9 @@ kv_decode_kernel(const KvDecodeParams p) {
   __shared__ float s_m[kKvDecWarps], s_l[kKvDecWarps];
   __shared__ __align__(16) float s_o[kKvDecWarps][kHeadDim];
   __shared__ float s_part[2 + kHeadDim];          // this CTA's share when a cluster splits the sequence: m, l, o[128]
+  // value codes of a warp's 32 tokens: lane = token brings its row in with 16-byte loads, lane = head dimensions reads
+  // two bytes per token from here (rows padded to 80 bytes: the 16-byte stores of a quarter-warp hit different banks)
+  __shared__ __align__(16) unsigned char s_v[kKvDecWarps][32][80];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x / p.splits;
   const int b = item / p.heads, head = item % p.heads;
@@ -206,8 +214,8 @@ kv_decode_kernel(const KvDecodeParams p) {
   const float qsum = s_qsum;
   const float sm_scale = 0.08838834764831845f * 1.4426950408889634f;   // log2(e) / sqrt(128)
 
-  float m = -INFINITY, l = 0.0f, zacc = 0.0f;
-  float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float m = -INFINITY, l = 0.0f, zacc = 0.0f, wsum = 0.0f;
+  float o[4] = {0.0f, 0.0f, 0.0f, 0.0f};       // sums of w * (8 + c / 2); wsum: the sum of the weights w = p * scale
   const size_t rows_per_page_kv = (size_t)p.heads * p.page_size;      // rows between the k and the v block of a page
   // the CTAs of a cluster take contiguous ranges of whole 32-token chunks
   const long long chunks = (seq_len + 31) >> 5;
@@ -217,39 +225,46 @@ kv_decode_kernel(const KvDecodeParams p) {
   for (long long base = tok_begin + (long long)warp * 32; base < tok_end; base += 32 * kKvDecWarps) {
     const long long t = base + lane;
     const bool valid = t < tok_end;
-    size_t krow = 0;
     float score = -INFINITY, vs = 0.0f, vz = 0.0f;
     if (valid) {
       const long long page = p.indices[first + (int)(t / p.page_size)];
       const int slot = (int)(t % p.page_size);
-      krow = ((((size_t)page * p.layers + p.layer) * 2) * p.heads + head) * p.page_size + slot;
+      const size_t krow = ((((size_t)page * p.layers + p.layer) * 2) * p.heads + head) * p.page_size + slot;
       const uint4* kp = reinterpret_cast<const uint4*>(p.data + krow * (kHeadDim / 2));
+      const uint4* vp = reinterpret_cast<const uint4*>(p.data + (krow + rows_per_page_kv) * (kHeadDim / 2));
+      uint4 kw[4], vw[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) kw[c] = __ldg(kp + c);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) vw[c] = __ldg(vp + c);      // requested with the keys, used after the scores
+      const float2 kpar = __half22float2(p.param[krow]);
+      const float2 vpar = __half22float2(p.param[krow + rows_per_page_kv]);
       float dot = 0.0f;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        const uint4 w = __ldg(kp + c);
-        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        const uint32_t ww[4] = {kw[c].x, kw[c].y, kw[c].z, kw[c].w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           // word i of chunk c holds elements 32 c + 8 i .. + 7, element e in bits [4e, 4e + 4)
           const float4 q0 = *reinterpret_cast<const float4*>(s_q + 32 * c + 8 * i);
           const float4 q1 = *reinterpret_cast<const float4*>(s_q + 32 * c + 8 * i + 4);
           // even elements are the low nibbles of the four bytes, odd elements the high nibbles
-          const uint32_t ev = ww[i] & 0x0F0F0F0Fu, od = (ww[i] >> 4) & 0x0F0F0F0Fu;
-          dot = fmaf(q0.x, byte_to_float<0>(ev), dot);
-          dot = fmaf(q0.y, byte_to_float<0>(od), dot);
-          dot = fmaf(q0.z, byte_to_float<1>(ev), dot);
-          dot = fmaf(q0.w, byte_to_float<1>(od), dot);
-          dot = fmaf(q1.x, byte_to_float<2>(ev), dot);
-          dot = fmaf(q1.y, byte_to_float<2>(od), dot);
-          dot = fmaf(q1.z, byte_to_float<3>(ev), dot);
-          dot = fmaf(q1.w, byte_to_float<3>(od), dot);
+          const uint32_t ev = (ww[i] << 3) & 0x78787878u, od = (ww[i] >> 1) & 0x78787878u;
+          dot = fmaf(q0.x, code_to_biased_float<0>(ev), dot);
+          dot = fmaf(q0.y, code_to_biased_float<0>(od), dot);
+          dot = fmaf(q0.z, code_to_biased_float<1>(ev), dot);
+          dot = fmaf(q0.w, code_to_biased_float<1>(od), dot);
+          dot = fmaf(q1.x, code_to_biased_float<2>(ev), dot);
+          dot = fmaf(q1.y, code_to_biased_float<2>(od), dot);
+          dot = fmaf(q1.z, code_to_biased_float<3>(ev), dot);
+          dot = fmaf(q1.w, code_to_biased_float<3>(od), dot);
         }
       }
-      const float2 kpar = __half22float2(p.param[krow]);
-      const float2 vpar = __half22float2(p.param[krow + rows_per_page_kv]);
+      dot = 2.0f * dot - 16.0f * qsum;            // sum of q * (8 + c / 2) -> sum of q * c
       score = (kpar.x * dot - kpar.y * qsum) * sm_scale;
       vs = vpar.x; vz = vpar.y;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) *reinterpret_cast<uint4*>(&s_v[warp][lane][16 * c]) = vw[c];
     }
     float cmax = score;
 #pragma unroll
@@ -265,41 +280,31 @@ kv_decode_kernel(const KvDecodeParams p) {
     }
     l = l * corr + psum;
     zacc = zacc * corr + pz;
+    wsum *= corr;
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[e] *= corr;
     m = m_new;
-    // values: lane = head dimensions 4 lane .. 4 lane + 3; token tt of the chunk broadcasts p * scale and its row
+    // values: lane = head dimensions 4 lane .. 4 lane + 3; token tt of the chunk broadcasts p * scale, its codes come
+    // from the warp's staging rows (the shuffles above have ordered the stores of all lanes before these loads)
     const float ps = pr * vs;
-    const size_t vrow = krow + rows_per_page_kv;
     const int ntok = (int)((tok_end - base) < 32 ? (tok_end - base) : 32);
-    // eight tokens at a time: their loads are all requested before the first is used (one 2-byte load per token and
-    // lane would otherwise wait for memory 32 times per chunk)
-#pragma unroll 1
-    for (int t0 = 0; t0 < ntok; t0 += 8) {
-      float wv[8];
-      uint32_t cv[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int tt = t0 + u;                       // tokens beyond the sequence carry weight 0 and the row of a valid one
-        wv[u] = __shfl_sync(0xffffffffu, ps, tt & 31);
-        const uint32_t rlo = __shfl_sync(0xffffffffu, (uint32_t)vrow, tt & 31);
-        const uint32_t rhi = __shfl_sync(0xffffffffu, (uint32_t)(vrow >> 32), tt & 31);
-        const size_t r = ((size_t)rhi << 32) | rlo;
-        cv[u] = __ldg(reinterpret_cast<const uint16_t*>(p.data + r * (kHeadDim / 2) + 2 * lane));
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const uint32_t ev = cv[u] & 0x0F0Fu, od = (cv[u] >> 4) & 0x0F0Fu;
-        o[0] = fmaf(wv[u], byte_to_float<0>(ev), o[0]);
-        o[1] = fmaf(wv[u], byte_to_float<0>(od), o[1]);
-        o[2] = fmaf(wv[u], byte_to_float<1>(ev), o[2]);
-        o[3] = fmaf(wv[u], byte_to_float<1>(od), o[3]);
-      }
+    __syncwarp();
+#pragma unroll 8
+    for (int tt = 0; tt < ntok; ++tt) {
+      const float wv = __shfl_sync(0xffffffffu, ps, tt);
+      const uint32_t cv = *reinterpret_cast<const uint16_t*>(&s_v[warp][tt][2 * lane]);
+      const uint32_t ev = (cv << 3) & 0x7878u, od = (cv >> 1) & 0x7878u;
+      wsum += wv;
+      o[0] = fmaf(wv, code_to_biased_float<0>(ev), o[0]);
+      o[1] = fmaf(wv, code_to_biased_float<0>(od), o[1]);
+      o[2] = fmaf(wv, code_to_biased_float<1>(ev), o[2]);
+      o[3] = fmaf(wv, code_to_biased_float<1>(od), o[3]);
     }
+    __syncwarp();      // the staging rows are rewritten by the next chunk
   }
-  // the zero points are the same for every head dimension
+  // back from w * (8 + c / 2) to w * c; the zero points are the same for every head dimension
 #pragma unroll
-  for (int e = 0; e < 4; ++e) o[e] -= zacc;
+  for (int e = 0; e < 4; ++e) o[e] = 2.0f * o[e] - 16.0f * wsum - zacc;
   if (lane == 0) { s_m[warp] = m; s_l[warp] = l; }
   *reinterpret_cast<float4*>(&s_o[warp][4 * lane]) = make_float4(o[0], o[1], o[2], o[3]);
   __syncthreads();
