@@ -1086,6 +1086,11 @@ int launch_gemm_i4_decode(const uint8_t* X, const uint8_t* W, int64_t M, int64_t
 size_t decode_stream_workspace_bytes(int64_t M, int64_t N, int64_t K);
 // weight-streaming mma.sync kernel for M <= 32 (gemv_mma_i4.cu)
 bool gemv_mma_serves(int64_t M, int64_t K);
+// 33 .. 64 token rows of a layer small enough that two passes of that kernel are the fastest form
+static bool gemv_two_pass(int64_t M, int64_t N, int64_t K) {
+  return g_tuning.gemv_mma_two_pass != 0 && g_tuning.gemv_mma_max_m >= 32 && M > 32 && M <= 64 &&
+         N * (K / 2) <= (int64_t)12 * 1024 * 1024 && gemv_mma_serves(32, K);
+}
 int launch_gemv_mma_i4(const uint8_t* A, const uint8_t* B, int64_t M, int64_t N, int64_t K, void* out, int64_t ldo,
                        const void* sA, const void* sB, const void* bias, bool f16, cudaStream_t st);
 // weight-streaming CUDA-core kernel for M <= 8 (gemv_i4.cu)
@@ -1187,6 +1192,17 @@ static int run_gemm(const char* who, const uint8_t* A, const uint8_t* B, int64_t
       rc = launch_gemv_mma_i4(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
       if (rc != QR_EUNSUPPORTED) return rc;
     }
+    // 33 .. 64 rows of a small layer (o_proj of a 7B model: 8 MB of weights): two passes of that kernel over the
+    // weights, 32 token rows each, beat the tcgen05 kernel below, whose MMA instruction count does not shrink with
+    // the layer (4096 x 4096 at 64 rows: 10.6 against 14.0 us; from about 12 MB on the single pass wins)
+    if (gemv_two_pass(M, N, K)) {
+      const size_t esz = MODE == MODE_F16 ? 2 : 4;
+      rc = launch_gemv_mma_i4(A, B, 32, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, st);
+      if (rc == QR_OK)
+        rc = launch_gemv_mma_i4(A + (size_t)32 * (K / 2), B, M - 32, N, K, reinterpret_cast<char*>(out) + (size_t)32 * ldo * esz, ldo,
+                                sA ? reinterpret_cast<const char*>(sA) + 64 : nullptr, sB, bias, MODE == MODE_F16, st);
+      if (rc != QR_EUNSUPPORTED) return rc;
+    }
     // decode-sized M on the tensor cores: weights on the MMA rows, all SMs streaming (gemm_i4_decode.cu)
     if (g_tuning.gemm_decode != 0) {
       rc = launch_gemm_i4_decode(A, B, M, N, K, out, ldo, sA, sB, bias, MODE == MODE_F16, grid_cap, ws, ws_bytes, st);
@@ -1246,6 +1262,7 @@ int qr_linear_i4_swiglu_f16(const uint8_t* A, const void* sA, const uint8_t* B, 
 size_t qr_linear_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   if (M <= qr::g_tuning.gemv_max_m || M > qr::g_tuning.gemm_decode_max_m || qr::g_tuning.gemm_decode == 0) return 0;
   if (M <= qr::g_tuning.gemv_mma_max_m && qr::gemv_mma_serves(M, K)) return 0;      // the mma.sync GEMV needs no scratch
+  if (qr::gemv_two_pass(M, N, K)) return 0;                                           // nor do two passes of it
   return qr::decode_stream_workspace_bytes(M, N, K);
 }
 

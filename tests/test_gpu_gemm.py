@@ -304,9 +304,10 @@ def test_workspace_argument_errors():
     _lib.set_tuning("gemv_mma_max_m", 32)                                 # the default: up to 32 rows without scratch
     assert _lib.lib.qr_linear_workspace_bytes(2, 4096, 4096) == 0
     assert _lib.lib.qr_linear_workspace_bytes(32, 4096, 4096) == 0
-    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 4096) > 0
+    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 4096) == 0       # a small layer: two passes of that kernel
+    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 8192) > 0
     _lib.set_tuning("gemm_splitk", 1)                                     # the default: scratch only for long rows
-    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 4096) == 0
+    assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 8192) == 0
     assert _lib.lib.qr_linear_workspace_bytes(33, 4096, 11008) > 0
     _lib.set_tuning("gemm_splitk", 2)
     assert _lib.lib.qr_linear_workspace_bytes(32, 4096, 28672) > 0       # rows too long for that kernel's shared memory
@@ -498,4 +499,31 @@ def test_weight_streaming_tensor_core_kernel(M, N, K):
     finally:
         _lib.set_tuning("gemv_max_m", 0)
         _lib.set_tuning("pdl", 2)
+    assert _lib.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 4096, 4096), (40, 1000, 2048), (33, 130, 320), (48, 260, 11008), (64, 7, 64)])
+def test_two_passes_of_the_weight_streaming_kernel(M, N, K):
+    """33 .. 64 token rows of a small layer run as two launches of the mma.sync kernel (32 rows, then the rest): exact
+    accumulators, the epilogue of the other kernels, an output pitch of its own; the same bits with the knob off
+    (the tcgen05 decode kernel)."""
+    g = torch.Generator().manual_seed(M * 7 + N)
+    a, w = _rand_packed(M, K, 11), _rand_packed(N, K, 12)
+    sx = (torch.rand(M, generator=g) * 0.5 + 0.05).half()
+    sw = (torch.rand(N, generator=g) * 0.015 + 0.005).half()
+    bias = (torch.randn(N, generator=g) * 0.5).half()
+    acc = O.matmul_i4(a, w)
+    ref = O.sym_dequant_fp32(acc, sx, sw).half()
+    ad, wd = a.to(DEV), w.to(DEV)
+    assert _lib.lib.qr_linear_workspace_bytes(M, N, K) == 0
+    try:
+        for knob in (1, 0):
+            _lib.set_tuning("gemv_mma_two_pass", knob)
+            assert torch.equal(qb.matmul(ad, wd).cpu(), acc)
+            assert torch.equal(qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), bias.to(DEV)).cpu(), ref + bias)
+            wide = torch.full((M, N + 5), 7.0, dtype=torch.float16, device=DEV)
+            qb.linear_i4(ad, sx.to(DEV), wd, sw.to(DEV), out=wide[:, :N])
+            assert torch.equal(wide[:, :N].cpu(), ref) and bool((wide[:, N:] == 7.0).all())
+    finally:
+        _lib.set_tuning("gemv_mma_two_pass", 1)
     assert _lib.kernel_status() == 0
