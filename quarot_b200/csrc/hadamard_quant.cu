@@ -531,6 +531,180 @@ hadq_fast_kernel(const HadqParams p) {
 }
 
 // ------------------------------------------------------------------ generic
+// ---------------------------------------------------------------------------------------------------------------
+// Few rows of n = 64 K (decode: the down_proj input of a 7B model, 11008 = 172 x 64): one row per CTA leaves the
+// GPU idle and the row's dense factor (K / 16 tiles x 8 x K / 16 MMAs) is what the CTA waits for.  Here a cluster of
+// four CTAs shares a row: every CTA stages the whole raw row but computes only its quarter of the factor's output
+// rows k', which it can finish by itself -- the Walsh transform runs along the 64 columns of each k' -- so the only
+// exchange is the row's absmax, four floats through distributed shared memory behind one cluster barrier per row.
+constexpr int kSplitCtas = 4;
+
+__device__ __forceinline__ uint32_t hq_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void hq_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float hq_peer_float(const float* p, uint32_t rank) {
+  uint32_t a = smem_u32(p), ra;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(a), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
+  return v;
+}
+
+// KT = 16-wide tiles of the dense factor; TPC = tiles per CTA = ceil(KT / 4); two warps per tile (four of the eight
+// 8-column MMA tiles each).  blockDim.x = 64 TPC.
+template <int KT>
+__global__ void __launch_bounds__(64 * ((KT + kSplitCtas - 1) / kSplitCtas))
+hadq_split_kernel(const HadqParams p) {
+  constexpr int TPC = (KT + kSplitCtas - 1) / kSplitCtas;
+  constexpr int kLocal = TPC * 16 * 64;                  // elements of a row this CTA produces
+  pdl_launch_dependents();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float s_red[2][32];
+  __shared__ float s_cmax[2];                            // this CTA's absmax of the current / the next row
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  const int K = p.K, n = p.n;
+  const uint32_t rank = hq_cluster_rank();
+  const int cluster_id = blockIdx.x / kSplitCtas, num_clusters = gridDim.x / kSplitCtas;
+  constexpr int pitch = 64 + 8;                          // halfs per staged k row
+  float* buf32 = reinterpret_cast<float*>(smem_raw);                       // [TPC * 16][64], swizzled
+  __half* raw = reinterpret_cast<__half*>(smem_raw + (size_t)kLocal * 4);  // [KT * 16][pitch]
+
+  // this warp's tile of the factor and its fragments (rows of the tile x all k)
+  const int mt = (int)rank * TPC + (warp >> 1);          // global tile
+  const int g = lane >> 2, t = lane & 3;
+  uint32_t afrag[KT][4];
+#pragma unroll
+  for (int kt = 0; kt < KT; ++kt) {
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int row = mt * 16 + g + ((r & 1) ? 8 : 0);
+      const int col = kt * 16 + 2 * t + ((r & 2) ? 8 : 0);
+      uint32_t val = 0;
+      if (row < K && col < K) val = *reinterpret_cast<const uint32_t*>(p.had_k + (size_t)row * K + col);
+      afrag[kt][r] = val;
+    }
+  }
+  auto stage_row = [&](int64_t r) {
+    const __half* xs = reinterpret_cast<const __half*>(p.x) + r * p.ldx;
+    for (int c = tid; c < (n >> 3); c += blockDim.x)
+      cp_async16(smem_u32(raw + (c >> 3) * pitch + ((c & 7) << 3)), xs + (size_t)c * 8);
+  };
+  for (int c = tid; c < (KT * 16 - K) * 8; c += blockDim.x)
+    *reinterpret_cast<uint4*>(raw + (K + (c >> 3)) * pitch + ((c & 7) << 3)) = make_uint4(0, 0, 0, 0);
+  pdl_wait();     // the table does not depend on the kernel in front, the activations do
+  if (cluster_id < p.rows) stage_row(cluster_id);
+
+  int parity = 0;
+  for (int64_t row = cluster_id; row < p.rows; row += num_clusters, parity ^= 1) {
+    cp_async_wait_all();
+    __syncthreads();
+    // ---- dense factor: this warp's 16 rows k' x 32 of the 64 columns
+    {
+      const int lrow = (lane & 7) + ((lane >> 3) & 1) * 8;
+      const int lcol = (lane >> 4) * 8;
+      const int half = warp & 1;
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f; }
+#pragma unroll
+      for (int kt = 0; kt < KT; ++kt) {
+#pragma unroll
+        for (int np = 0; np < 2; ++np) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b, smem_u32(raw + (kt * 16 + lrow) * pitch + (2 * half + np) * 16 + lcol));
+          mma_16816(acc[2 * np], afrag[kt], b[0], b[1]);
+          mma_16816(acc[2 * np + 1], afrag[kt], b[2], b[3]);
+        }
+      }
+      const int r0 = (warp >> 1) * 16 + g;               // local row
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        const int col = half * 32 + nt * 8 + 2 * t;
+        *reinterpret_cast<float2*>(buf32 + phys(r0 * 64 + col)) = make_float2(acc[nt][0], acc[nt][1]);
+        *reinterpret_cast<float2*>(buf32 + phys((r0 + 8) * 64 + col)) = make_float2(acc[nt][2], acc[nt][3]);
+      }
+    }
+    __syncthreads();
+    if (row + num_clusters < p.rows) stage_row(row + num_clusters);   // every warp is done with the staging buffer
+    // ---- Walsh over the 64 columns: bit 5 through shared memory, bits 0 .. 4 in registers
+    pass_b5<1>(buf32, kLocal, tid, blockDim.x);
+    __syncthreads();
+    __half2 h[16];
+    float amax = 0.0f;
+    const int kprime = (int)rank * TPC * 16 + (tid >> 1);      // the factor's output row of this thread's 32 elements
+    const bool live = tid < (kLocal >> 5) && kprime < K;
+    if (tid < (kLocal >> 5)) {
+      float v[32];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const float4 f = *reinterpret_cast<const float4*>(buf32 + tid * 32 + ((s ^ (tid & 7)) << 2));
+        v[4 * s] = f.x; v[4 * s + 1] = f.y; v[4 * s + 2] = f.z; v[4 * s + 3] = f.w;
+      }
+      fwht_regs<32>(v);
+      __half2 mx = __float2half2_rn(0.0f);
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        h[e] = __floats2half2_rn(v[2 * e] * p.scale, v[2 * e + 1] * p.scale);
+        mx = __hmax2(mx, __habs2(h[e]));
+      }
+      const float2 mf = __half22float2(mx);
+      if (live) amax = fmaxf(mf.x, mf.y);
+      if (live && p.y_out) {
+        uint4* yo = reinterpret_cast<uint4*>(reinterpret_cast<__half*>(p.y_out) + row * (int64_t)n + (size_t)kprime * 64 + (tid & 1) * 32);
+#pragma unroll
+        for (int s = 0; s < 4; ++s) yo[s] = *reinterpret_cast<const uint4*>(&h[4 * s]);
+      }
+    }
+    // ---- the row's absmax: CTA-wide, then over the four CTAs
+    const float a_cta = block_absmax(amax, s_red[parity], lane, warp, nwarps);
+    if (tid == 0) s_cmax[parity] = a_cta;
+    hq_cluster_sync();
+    float a = 0.0f;
+#pragma unroll
+    for (uint32_t r = 0; r < (uint32_t)kSplitCtas; ++r) a = fmaxf(a, hq_peer_float(&s_cmax[parity], r));
+    const float s = scale_from_absmax(a, p.clip, (tid == 0 && rank == 0) ? p.scales + row : nullptr);
+    const float rcp = (s != 0.0f) ? __frcp_rn(s) : 0.0f;
+    if (live)
+      *reinterpret_cast<uint4*>(p.q + row * (int64_t)(n >> 1) + (size_t)kprime * 32 + (tid & 1) * 16) = quant32(h, s, rcp, clamp_free(s, p.clip));
+  }
+  hq_cluster_sync();      // nobody leaves while a peer may still read its absmax
+}
+
+template <int KT>
+static int launch_split(const HadqParams& p, cudaStream_t st) {
+  constexpr int TPC = (KT + kSplitCtas - 1) / kSplitCtas;
+  const size_t smem = (size_t)TPC * 16 * 64 * 4 + (size_t)KT * 16 * (64 + 8) * 2;
+  static thread_local size_t configured[64] = {0};
+  int dev = 0;
+  QR_CUDA(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (dev >= 64 || configured[dev] < smem)) {
+    QR_CUDA(cudaFuncSetAttribute(hadq_split_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev < 64) configured[dev] = smem;
+  }
+  int64_t clusters = p.rows;
+  const int64_t cap = (int64_t)num_sms() / 2; // two CTAs per SM are resident at 148 registers; more rows than clusters walk the rows
+  if (clusters > cap) clusters = cap;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(clusters * kSplitCtas));
+  cfg.blockDim = dim3(64 * TPC);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kSplitCtas; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = use_pdl(p.rows) ? 2 : 1;
+  QR_CUDA(cudaLaunchKernelEx(&cfg, hadq_split_kernel<KT>, p));
+  return QR_OK;
+}
+
 template <typename T> __device__ __forceinline__ float load_as_float(const T* p, int64_t i);
 template <> __device__ __forceinline__ float load_as_float<__half>(const __half* p, int64_t i) { return __half2float(p[i]); }
 template <> __device__ __forceinline__ float load_as_float<float>(const float* p, int64_t i) { return p[i]; }
@@ -709,6 +883,18 @@ static int run_hadq(const char* who, const void* x, int64_t rows, int64_t n64, i
     QR_CUDA(launch_kernel(quant_rows_kernel<4, true>, dim3(persistent_grid(rows, threads, 1024)), dim3(threads), 0, st,
                           use_pdl(p.rows), p));
     return QR_OK;
+  }
+  // few rows of n = 64 K with the quantiser behind: a cluster of four CTAs per row
+  // (11008 = 172 x 64: 3.8 against 5.2 us for one row, 4.0 against 5.3 us for eight, 4.8 against 5.5 us for 32; from
+  // 64 rows on one CTA per row is as fast, and every CTA of a cluster stages the whole row)
+  if (base_ok && K > 1 && m == 64 && ldx == n && do_quant && rows <= 32 && g_tuning.hadq_split != 0) {
+    switch (kt_for(K)) {
+      case 7: return launch_split<7>(p, st);
+      case 9: return launch_split<9>(p, st);
+      case 10: return launch_split<10>(p, st);
+      case 11: return launch_split<11>(p, st);
+      default: break;
+    }
   }
   // (below 129 rows the persistent tensor-core kernel's set-up is not amortised: 7.2 against 6.4 us at 8 rows of 11008)
   if (base_ok && K > 1 && m == 64 && ldx == n && (rows > 128 || g_tuning.hadq_tc == 2) && g_tuning.hadq_tc != 0) {

@@ -141,7 +141,8 @@ def test_hadamard_random_vs_oracle_all_families(n, rows):
 @pytest.mark.parametrize("n,K,rows", [(256, 0, 5), (4096, 0, 17), (11008, 0, 3), (22016 // 2, 0, 2), (96, 0, 3),
                                       (4096, 1, 17), (1024, 1, 4), (8192, 1, 2), (64, 1, 9), (256, 1, 5),
                                       (11008, 172, 9), (28672, 28, 3), (13824, 108, 2), (344, 172, 3),
-                                      (112, 28, 4)])
+                                      (112, 28, 4), (6912, 108, 5), (8960, 140, 3), (9984, 156, 7), (11008, 172, 32),
+                                      (11008, 172, 1), (11008, 172, 40)])
 @pytest.mark.parametrize("clip", [1.0, 0.9])
 def test_fused_hadamard_quant_bit_exact_given_own_hadamard(n, K, rows, clip):
     x = synth.activations(rows, n, seed=7 * n + K)
@@ -160,6 +161,30 @@ def test_fused_hadamard_quant_bit_exact_given_own_hadamard(n, K, rows, clip):
     # without the side output the codes are the same
     q2, s2, none = qb.hadamard_quant(x.to(DEV), table, K, clip)
     assert none is None and torch.equal(q2.cpu(), q) and torch.equal(_bits(s2), _bits(s))
+
+
+@pytest.mark.parametrize("n,K,rows", [(11008, 172, 1), (11008, 172, 8), (11008, 172, 32), (6912, 108, 6), (8960, 140, 2),
+                                      (9984, 156, 11)])
+def test_few_rows_shared_by_a_cluster_give_the_bits_of_one_cta_per_row(n, K, rows):
+    """Up to 32 rows of n = 64 K are transformed by clusters of four CTAs that share a row (each a quarter of the dense
+    factor's output rows, the absmax exchanged through distributed shared memory): the same Hadamard output, scales
+    and codes as with one CTA per row, also over repeated launches."""
+    x = synth.activations(rows, n, seed=n + rows).to(DEV)
+    x[0, :5] = 0
+    table = FH.device_table(K, DEV)
+    try:
+        _lib.set_tuning("hadq_tc", 1)          # the reference form is the mma.sync kernel with one CTA per row
+        _lib.set_tuning("hadq_split", 0)
+        q0, s0, y0 = qb.hadamard_quant(x, table, K, 0.9, return_y=True)
+        _lib.set_tuning("hadq_split", 1)
+        for _ in range(2):
+            q1, s1, y1 = qb.hadamard_quant(x, table, K, 0.9, return_y=True)
+            assert torch.equal(_bits(y1), _bits(y0)) and torch.equal(_bits(s1), _bits(s0)) and torch.equal(q1, q0)
+        q2, s2, _ = qb.hadamard_quant(x, table, K, 0.9)
+        assert torch.equal(q2, q0) and torch.equal(_bits(s2), _bits(s0))
+    finally:
+        _lib.set_tuning("hadq_split", 1)
+    assert _lib.kernel_status() == 0
 
 
 def test_division_by_reciprocal_gives_ieee_codes_for_every_fp16_pair():
