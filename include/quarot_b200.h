@@ -55,7 +55,10 @@ int qr_kernel_status(int* status_out);
 
 /* Kernel-selection knobs, process-wide: "gemm_bn", "gemm_bn2", "gemm_pst", "gemm_grid", "gemm_decode_max_m",
  * "gemm_decode", "gemm_splitk", "gemm_2sm", "gemm_tma_out", "gemm_tail_help", "gemv_max_m", "gemv_mma_max_m", "gemv_mma_halves", "gemv_mma_two_pass", "pdl", "hadq_path",
- * "hadq_tc", "hadq_split", "hadq_walsh".  Every setting computes the same results; the defaults are the measured best choices.  Unknown keys
+ * "hadq_tc", "hadq_split", "hadq_heads", "hadq_walsh".  The "gemm_*", "gemv_*" and "pdl" settings never change a bit of a
+ * result; the "hadq_*" settings choose between Hadamard kernels that add in different orders, whose fp16 outputs agree
+ * within the rounding of the transform (codes and scales are always exact for the output that was produced).  The
+ * defaults are the measured best choices.  Unknown keys
  * return QR_EINVAL.  No upstream counterpart. */
 int qr_set_tuning(const char* key, int value);
 

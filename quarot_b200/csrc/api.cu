@@ -94,7 +94,7 @@ int qr_set_tuning(const char* key, int value) {
       {"pdl", &qr::Tuning::pdl},                   {"hadq_path", &qr::Tuning::hadq_path},
       {"hadq_tc", &qr::Tuning::hadq_tc},           {"gemm_decode", &qr::Tuning::gemm_decode},
       {"gemm_bn2", &qr::Tuning::gemm_bn2},         {"hadq_walsh", &qr::Tuning::hadq_walsh},
-      {"gemv_mma_max_m", &qr::Tuning::gemv_mma_max_m}, {"gemv_mma_halves", &qr::Tuning::gemv_mma_halves}, {"gemv_mma_two_pass", &qr::Tuning::gemv_mma_two_pass}, {"hadq_split", &qr::Tuning::hadq_split}, {"gemm_tail_help", &qr::Tuning::gemm_tail_help},
+      {"gemv_mma_max_m", &qr::Tuning::gemv_mma_max_m}, {"gemv_mma_halves", &qr::Tuning::gemv_mma_halves}, {"gemv_mma_two_pass", &qr::Tuning::gemv_mma_two_pass}, {"hadq_split", &qr::Tuning::hadq_split}, {"hadq_heads", &qr::Tuning::hadq_heads}, {"gemm_tail_help", &qr::Tuning::gemm_tail_help},
   };
   if (!key) return qr::fail(QR_EINVAL, "qr_set_tuning: null key");
   for (const auto& k : known) {

@@ -30,7 +30,8 @@ struct Tuning {
   int gemm_tail_help = 1;     // 2-CTA kernel: idle warps share the epilogue of a CTA's last tile
   int gemv_max_m = 0;         // token rows up to which the weight-streaming CUDA-core (dp4a) kernel is used (it also serves the quantiser-fused call)
   int gemv_mma_halves = 0;    // that kernel as two CTAs of eight warps per SM (1, where they fit) or one of sixteen (2); 0: the measured choice
-  int hadq_split = 1;         // up to 128 rows of n = 64 K: a cluster of four CTAs per row (0: one CTA per row)
+  int hadq_heads = 1;         // heads-axis Hadamard of 8, 16 or 32 heads: two columns per thread (0: the masked warp-per-row kernel)
+  int hadq_split = 1;         // up to 32 rows of n = 64 K: a cluster of four CTAs per row (0: one CTA per row)
   int gemv_mma_two_pass = 1;  // 33 .. 64 token rows of layers of at most 12 MB: two passes of that kernel instead of the tcgen05 decode kernel
   int gemv_mma_max_m = 32;    // token rows up to which the weight-streaming mma.sync kernel is used (0: never)
   int gemm_decode = 1;        // decode: the weight-streaming tcgen05 kernel (0: tokens on the MMA rows as at prefill)

@@ -36,6 +36,10 @@ namespace qr {
 int launch_hadq_tc(const void* x, int64_t rows, int n, int K, const void* had_k, float clip, uint8_t* q,
                    void* scales, void* y_out, int do_quant, cudaStream_t st);
 
+// heads-axis transform of [rows, heads, head_dim] with two columns per thread (hadamard_walsh.cu); QR_EUNSUPPORTED
+// means "not my shape"
+int launch_hadq_heads(const void* x, void* y, int64_t rows, int heads, int head_dim, cudaStream_t st);
+
 // warp-per-row Walsh kernel for n = 256 .. 4096 (hadamard_walsh.cu); QR_EUNSUPPORTED means "not my shape"
 int launch_hadq_walsh(const void* x, int64_t rows, int n, int64_t ldx, uint32_t stage_mask, float scale, float clip,
                       uint8_t* q, void* scales, void* y_out, int64_t ldy, int do_quant, cudaStream_t st);
@@ -975,6 +979,10 @@ int qr_hadamard_heads_f16(const void* x, void* y, int64_t rows, int64_t heads, i
   if (!qr::is_pow2(heads) || !qr::is_pow2(head_dim) || head_dim < 32 || n < 256 || n > 4096)
     return qr::fail(QR_EUNSUPPORTED, "qr_hadamard_heads_f16: heads = %lld, head_dim = %lld (powers of two, head_dim >= 32, "
                     "256 <= heads x head_dim <= 4096)", (long long)heads, (long long)head_dim);
+  if (qr::g_tuning.hadq_heads != 0 && qr::aligned16(x) && qr::aligned16(y)) {
+    const int rc2 = qr::launch_hadq_heads(x, y, rows, (int)heads, (int)head_dim, (cudaStream_t)stream);
+    if (rc2 != QR_EUNSUPPORTED) return rc2;
+  }
   const uint32_t mask = (uint32_t)((heads - 1) * head_dim);      // the index bits of the heads axis
   const int rc = qr::launch_hadq_walsh(x, rows, (int)n, n, mask, (float)(1.0 / sqrt((double)heads)), 1.0f, nullptr, nullptr,
                                        y, n, 0, (cudaStream_t)stream);
