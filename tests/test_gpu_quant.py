@@ -305,6 +305,18 @@ def test_heads_axis_hadamard_on_the_transposed_view(heads, head_dim):
     assert back.shape == (2, 37, heads * head_dim)
     if 256 <= heads * head_dim <= 4096 and head_dim >= 32:
         assert y.transpose(-1, -2).is_contiguous()      # no copy on the way back either
+        # the C entry point in place (y may alias x): the same bits; the other heads-axis kernel: the same values within
+        # the rounding of the transform
+        inplace = attn.clone()
+        _lib.check(_lib.lib.qr_hadamard_heads_f16(inplace.data_ptr(), inplace.data_ptr(), 2 * 37, heads, head_dim, None), "heads")
+        assert torch.equal(inplace, y.transpose(-1, -2))
+        _lib.set_tuning("hadq_heads", 0)
+        try:
+            other = qb.nn.OnlineHadamard(heads).to(DEV)(view)
+        finally:
+            _lib.set_tuning("hadq_heads", 1)
+        ok, worst = _had_close(other.cpu().contiguous(), ref)
+        assert ok, worst
 
 
 @pytest.mark.parametrize("n,rows", [(256, 7), (512, 3), (1024, 50), (2048, 13), (4096, 29)])
