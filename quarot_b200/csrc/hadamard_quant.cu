@@ -249,7 +249,10 @@ struct RmsQuantParams {
   __half* y_out;     // optional copy of the normalised row, or null
 };
 
-__global__ void __launch_bounds__(1024)
+// CPT = 16-byte chunks per thread: 4 for persistent CTAs that walk the rows, 8 for one small CTA per row where every row
+// of the call can be resident at once (as in quant_rows_kernel).
+template <int CPT>
+__global__ void __launch_bounds__(CPT == 8 ? 512 : 1024)
 rmsnorm_quant_rows_kernel(const RmsQuantParams p) {
   __shared__ float red_max[2][32];
   __shared__ float red_ss[2][32];
@@ -259,12 +262,12 @@ rmsnorm_quant_rows_kernel(const RmsQuantParams p) {
   int parity = 0;
   for (int64_t row = blockIdx.x; row < p.rows; row += gridDim.x, parity ^= 1) {
     const uint4* xr = reinterpret_cast<const uint4*>(p.x + row * p.ldx);
-    uint4 cur[4];
+    uint4 cur[CPT];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xr + tid + j * T) : zero;
+    for (int j = 0; j < CPT; ++j) cur[j] = (tid + j * T < nchunks) ? __ldg(xr + tid + j * T) : zero;
     float amax = 0.0f, ss = 0.0f;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < CPT; ++j) {
       const __half2* h = reinterpret_cast<const __half2*>(&cur[j]);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -296,7 +299,7 @@ rmsnorm_quant_rows_kernel(const RmsQuantParams p) {
     uint32_t* qo = reinterpret_cast<uint32_t*>(p.q + row * (int64_t)(p.n >> 1));
     uint4* yo = p.y_out ? reinterpret_cast<uint4*>(p.y_out + row * (int64_t)p.n) : nullptr;
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < CPT; ++j) {
       const int c = tid + j * T;
       if (c < nchunks) {
         const __half2* h = reinterpret_cast<const __half2*>(&cur[j]);
@@ -1011,8 +1014,13 @@ int qr_rmsnorm_quant_i4(const void* x, int64_t rows, int64_t n, int64_t ldx, int
   p.x = reinterpret_cast<const __half*>(x); p.ldx = ldx; p.rows = rows; p.n = (int)n;
   p.eps = eps; p.mean_dim = (float)mean_dim; p.clip = clip;
   p.q = q; p.scales = reinterpret_cast<__half*>(scales); p.y_out = reinterpret_cast<__half*>(y_out);
+  const int threads8 = (((int)n / 8 + 7) / 8 + 31) / 32 * 32;
+  if (rows >= 256 && rows <= (int64_t)qr::num_sms() * 16 && threads8 <= 512 && rows * (int64_t)threads8 <= (int64_t)qr::num_sms() * 1536) {
+    QR_CUDA(qr::launch_kernel(qr::rmsnorm_quant_rows_kernel<8>, dim3((unsigned)rows), dim3(threads8), 0, (cudaStream_t)stream, false, p));
+    return QR_OK;
+  }
   int threads = (((int)n / 8 + 3) / 4 + 31) / 32 * 32;
-  QR_CUDA(qr::launch_kernel(qr::rmsnorm_quant_rows_kernel, dim3(qr::persistent_grid(rows, threads, 1024)), dim3(threads), 0,
+  QR_CUDA(qr::launch_kernel(qr::rmsnorm_quant_rows_kernel<4>, dim3(qr::persistent_grid(rows, threads, 1024)), dim3(threads), 0,
                             (cudaStream_t)stream, false, p));
   return QR_OK;
 }
